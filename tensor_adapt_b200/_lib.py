@@ -1,0 +1,128 @@
+"""ctypes binding of libtensor_adapt_b200.so (the C ABI declared in include/tensor_adapt_b200.h).
+
+The library is the product; this module only loads it and checks return codes.  There is no
+Python or CPU fallback: if the shared library is missing or fails to load, importing raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_long, c_size_t, c_void_p
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libtensor_adapt_b200.so")
+
+TA_OK = 0
+ERR_NAMES = {-1: "TA_ERR_INVALID", -2: "TA_ERR_CUDA", -3: "TA_ERR_UNSUPPORTED", -4: "TA_ERR_DEVICE_TIMEOUT",
+             -5: "TA_ERR_NOMEM", -6: "TA_ERR_IO"}
+
+
+class TAError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"{ERR_NAMES.get(code, code)}: {msg}")
+        self.code = code
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is not built. Run `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(or `make -C tensor_adapt_b200`); there is no fallback implementation.")
+    # torch first, so that libcudart / libnccl resolve to the copies torch already mapped
+    try:
+        import torch  # noqa: F401
+    except Exception:
+        pass
+    return ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+
+
+lib = _load()
+
+P = c_void_p
+_PROTOS = {
+    "ta_ctx_create": (c_int, [c_int, POINTER(c_void_p)]),
+    "ta_ctx_destroy": (c_int, [P]),
+    "ta_ctx_set_workspace": (c_int, [P, P, c_size_t]),
+    "ta_last_error": (c_char_p, [P]),
+    "ta_device_status": (c_int, [P, POINTER(c_int)]),
+    "ta_launch_count": (c_long, [P]),
+    "ta_rms_norm_fwd": (c_int, [P, P, P, P, P, c_int, c_int, c_float, P]),
+    "ta_rms_norm_bwd": (c_int, [P, P, P, P, P, P, P, c_int, c_int, P]),
+    "ta_rope": (c_int, [P, P, c_int, P, c_int, c_int, c_int, c_int, c_float, c_int, P]),
+    "ta_silu_mul_fwd": (c_int, [P, P, P, P, c_long, P]),
+    "ta_silu_mul_bwd": (c_int, [P, P, P, P, P, P, c_long, P]),
+    "ta_cross_entropy_fwd": (c_int, [P, P, P, P, P, c_int, c_int, c_float, P]),
+    "ta_embed_fwd": (c_int, [P, P, P, P, c_int, c_int, P]),
+    "ta_add_bias": (c_int, [P, P, P, c_long, c_int, P]),
+    "ta_add_inplace": (c_int, [P, P, P, c_long, P]),
+    "ta_lora_add": (c_int, [P, P, P, c_float, c_long, P]),
+    "ta_cast_bf16_to_f32": (c_int, [P, P, P, c_long, P]),
+    "ta_cast_f32_to_bf16": (c_int, [P, P, P, c_long, P]),
+    "ta_gemm_bf16": (c_int, [P, c_int, c_int, c_int, c_float, P, c_long, c_int, P, c_long, c_int, P, P, P, c_long, P]),
+    "ta_gemm_tokens_f32": (c_int, [P, c_int, c_int, c_int, c_float, P, c_long, P, c_long, P, c_long, c_int, c_int, P]),
+}
+
+
+def declare(protos) -> None:
+    for name, (res, args) in protos.items():
+        fn = getattr(lib, name)   # AttributeError here = the .so does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+
+
+declare(_PROTOS)
+
+
+def exported_symbols():
+    """Names this binding expects the library to export (tests compare them with include/*.h)."""
+    return sorted(_PROTOS)
+
+
+class Context:
+    """Owns a `ta_ctx*`; `call(name, *args)` invokes an entry point whose first parameter is the
+    context and raises TAError with the library's message on a non-zero return."""
+
+    def __init__(self, device: int = 0):
+        h = c_void_p()
+        rc = lib.ta_ctx_create(device, ctypes.byref(h))
+        if rc != TA_OK:
+            raise TAError(rc, f"ta_ctx_create(device={device}) failed: an sm_100 (B200) GPU is required")
+        self.h = h
+        self.device = device
+
+    def call(self, name: str, *args):
+        rc = getattr(lib, name)(self.h, *args)
+        if rc != TA_OK:
+            raise TAError(rc, (lib.ta_last_error(self.h) or b"").decode())
+        return rc
+
+    def check_device(self) -> None:
+        st = c_int(0)
+        rc = lib.ta_device_status(self.h, ctypes.byref(st))
+        if rc != TA_OK:
+            raise TAError(rc, f"device status {st.value}: {(lib.ta_last_error(self.h) or b'').decode()}")
+
+    @property
+    def launches(self) -> int:
+        return int(lib.ta_launch_count(self.h))
+
+    def close(self) -> None:
+        if self.h:
+            lib.ta_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def ptr(t) -> c_void_p:
+    """Device pointer of a torch tensor (or None)."""
+    return c_void_p(0) if t is None else c_void_p(t.data_ptr())
+
+
+def stream_ptr() -> c_void_p:
+    import torch
+    return c_void_p(torch.cuda.current_stream().cuda_stream)

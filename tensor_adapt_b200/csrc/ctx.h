@@ -1,0 +1,77 @@
+// Library context: device, status word for bounded device waits, scratch workspace and the
+// tensor-map cache used by the TMA-fed kernels.  Internal header (the C ABI sees `ta_ctx` opaquely).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstddef>
+#include <string>
+#include <unordered_map>
+
+#include "../../include/tensor_adapt_b200.h"
+
+namespace ta {
+
+struct TmapKey {
+    const void* ptr;
+    uint64_t dim0, dim1, pitch_bytes;
+    uint32_t box0, box1;
+    bool operator==(const TmapKey& o) const {
+        return ptr == o.ptr && dim0 == o.dim0 && dim1 == o.dim1 && pitch_bytes == o.pitch_bytes && box0 == o.box0 &&
+               box1 == o.box1;
+    }
+};
+struct TmapKeyHash {
+    size_t operator()(const TmapKey& k) const {
+        uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.dim0 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+        h ^= (k.dim1 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+        h ^= (k.pitch_bytes + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+        h ^= ((uint64_t(k.box0) << 32 | k.box1) + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+        return static_cast<size_t>(h);
+    }
+};
+
+}  // namespace ta
+
+struct ta_ctx {
+    int device = 0;
+    int sm_count = 148;
+    int* d_status = nullptr;        // device word written by kernels whose waits ran out
+    void* ws = nullptr;             // scratch workspace (split-K partials, reduction partials)
+    size_t ws_bytes = 0;
+    bool ws_owned = false;
+    std::string last_error;
+    std::unordered_map<ta::TmapKey, CUtensorMap, ta::TmapKeyHash> tmaps;
+    long launches = 0;              // kernels launched through this context (bench.py's gpu_launches)
+};
+
+namespace ta {
+
+int fail(ta_ctx* ctx, int code, const std::string& msg);
+int check_cuda(ta_ctx* ctx, cudaError_t e, const char* what);
+
+// Cached 2-D BF16 tensor map with 128-byte swizzle: tensor [dim1 rows][dim0 cols], row pitch in bytes,
+// box [box1 rows][box0 cols]; out-of-bounds elements read as zero.
+int get_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0,
+                  uint32_t box1, CUtensorMap* out);
+
+// Scratch of at least `bytes`, grown on demand when the context owns its workspace.
+int get_workspace(ta_ctx* ctx, size_t bytes, void** out);
+
+}  // namespace ta
+
+#define TA_CUDA(ctx, call)                                              \
+    do {                                                                \
+        cudaError_t _e = (call);                                        \
+        if (_e != cudaSuccess) return ta::check_cuda((ctx), _e, #call); \
+    } while (0)
+
+#define TA_LAUNCH_CHECK(ctx, name)                                      \
+    do {                                                                \
+        cudaError_t _e = cudaGetLastError();                            \
+        if (_e != cudaSuccess) return ta::check_cuda((ctx), _e, name);  \
+        if (ctx) (ctx)->launches++;                                     \
+    } while (0)

@@ -1,0 +1,416 @@
+// Segmented-K BF16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma with the
+// FP32 accumulator in TMEM -> tcgen05.ld epilogue (alpha, bias, residual, BF16/FP32 store).
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocator + MMA issuer (one elected lane)
+//   warps 2-5   epilogue: warp w owns TMEM lanes 32*(w%4) .. +31, i.e. 32 rows of the 128-row tile
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
+// main loop of tile i+1.  All waits are bounded (see ptx.cuh).
+#include "seg_gemm.h"
+
+#include <algorithm>
+#include <cstring>
+
+#include "ptx.cuh"
+
+namespace ta {
+
+namespace {
+
+struct alignas(64) SegGemmParams {
+    CUtensorMap tmA[kMaxSegments];
+    CUtensorMap tmB[kMaxSegments];
+    int K[kMaxSegments];
+    int a_mn[kMaxSegments];
+    int b_mn[kMaxSegments];
+    int nseg, M, N;
+    int split_k, kb_per_split;
+    void* C;
+    long ldc;
+    int f32, accumulate;
+    float alpha;
+    const __nv_bfloat16* bias;
+    const __nv_bfloat16* residual;
+    float* ws;
+    long ws_split_stride;
+    int* status;
+};
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GROUP_M = 16;   // m-tiles per raster group: a wave touches ~16 A tiles and ~9 B tiles -> L2 reuse
+
+template <int BN>
+struct Cfg {
+    static constexpr uint32_t A_BYTES = BM * BK * 2;
+    static constexpr uint32_t B_BYTES = (BN < 64 ? 64 : BN) * BK * 2;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+    static constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+    static constexpr int NCHUNK_B = (BN + 63) / 64;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+};
+
+struct TileCoord {
+    int m0, n0, split;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_tiles, int bn) {
+    const int per_split = m_tiles * n_tiles;
+    TileCoord t;
+    t.split = tile / per_split;
+    int rem = tile - t.split * per_split;
+    const int per_group = GROUP_M * n_tiles;
+    const int g = rem / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(GROUP_M, m_tiles - first_m);
+    const int in_g = rem - g * per_group;
+    t.m0 = (first_m + in_g % gsz) * BM;
+    t.n0 = (in_g / gsz) * bn;
+    return t;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant__ SegGemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* tfull = empty + C::STAGES;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int m_tiles = (p.M + BM - 1) / BM;
+    const int n_tiles = (p.N + BN - 1) / BN;
+    const int total = m_tiles * n_tiles * p.split_k;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int s = 0; s < p.nseg; s++) {
+                prefetch_tensormap(&p.tmA[s]);
+                prefetch_tensormap(&p.tmB[s]);
+            }
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, BN);
+                for (int s = 0; s < p.nseg; s++) {
+                    const int nkb = (p.K[s] + BK - 1) / BK;
+                    int kb_lo = 0, kb_hi = nkb;
+                    if (p.split_k > 1) {
+                        kb_lo = tc.split * p.kb_per_split;
+                        kb_hi = min(nkb, kb_lo + p.kb_per_split);
+                    }
+                    const bool a_mn = p.a_mn[s] != 0, b_mn = p.b_mn[s] != 0;
+                    const uint32_t tx = C::A_BYTES + (b_mn ? C::NCHUNK_B * 8192u : uint32_t(BN) * 128u);
+                    for (int kb = kb_lo; kb < kb_hi; kb++, it++) {
+                        const uint32_t stage = it % C::STAGES;
+                        const uint32_t ph = (it / C::STAGES) & 1u;
+                        if (!mbar_wait(&empty[stage], ph ^ 1u, abort_flag, p.status, DS_TIMEOUT_PRODUCER)) goto done;
+                        uint8_t* sa = smem + stage * C::STAGE_BYTES;
+                        uint8_t* sb = sa + C::A_BYTES;
+                        mbar_arrive_expect_tx(&full[stage], tx);
+                        if (!a_mn) {
+                            tma_load_2d(sa, &p.tmA[s], &full[stage], kb * BK, tc.m0);
+                        } else {
+                            tma_load_2d(sa, &p.tmA[s], &full[stage], tc.m0, kb * BK);
+                            tma_load_2d(sa + 8192, &p.tmA[s], &full[stage], tc.m0 + 64, kb * BK);
+                        }
+                        if (!b_mn) {
+                            tma_load_2d(sb, &p.tmB[s], &full[stage], kb * BK, tc.n0);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < C::NCHUNK_B; c++)
+                                tma_load_2d(sb + c * 8192, &p.tmB[s], &full[stage], tc.n0 + 64 * c, kb * BK);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t it = 0, lt = 0;
+            for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, BN);
+                const uint32_t buf = lt & 1u, use = lt >> 1;
+                if (!mbar_wait(&tempty[buf], (use & 1u) ^ 1u, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
+                tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                uint32_t acc = 0;
+                for (int s = 0; s < p.nseg; s++) {
+                    const int nkb = (p.K[s] + BK - 1) / BK;
+                    int kb_lo = 0, kb_hi = nkb;
+                    if (p.split_k > 1) {
+                        kb_lo = tc.split * p.kb_per_split;
+                        kb_hi = min(nkb, kb_lo + p.kb_per_split);
+                    }
+                    const bool a_mn = p.a_mn[s] != 0, b_mn = p.b_mn[s] != 0;
+                    const uint32_t idesc = umma_idesc_bf16(BM, BN, a_mn, b_mn);
+                    for (int kb = kb_lo; kb < kb_hi; kb++, it++) {
+                        const uint32_t stage = it % C::STAGES;
+                        const uint32_t ph = (it / C::STAGES) & 1u;
+                        if (!mbar_wait(&full[stage], ph, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
+                        tcgen05_fence_after_sync();
+                        const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                        const uint32_t sb = sa + C::A_BYTES;
+                        const int krem = p.K[s] - kb * BK;
+                        const int kinstr = krem >= BK ? 4 : (krem + 15) / 16;
+                        for (int ki = 0; ki < kinstr; ki++) {
+                            const uint64_t ad = a_mn ? smem_desc_sw128(sa + ki * 2048, 8192, 1024)
+                                                     : smem_desc_sw128(sa + ki * 32, 16, 1024);
+                            const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
+                                                     : smem_desc_sw128(sb + ki * 32, 16, 1024);
+                            umma_bf16(d_tmem, ad, bd, idesc, acc);
+                            acc = 1;
+                        }
+                        umma_commit(&empty[stage]);
+                    }
+                }
+                umma_commit(&tfull[buf]);
+            }
+        }
+    } else {
+        const int lg = warp & 3;   // TMEM lane group this warp may access
+        uint32_t lt = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, BN);
+            const uint32_t buf = lt & 1u, use = lt >> 1;
+            if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
+            tcgen05_fence_after_sync();
+            const int row = tc.m0 + lg * 32 + lane;
+            const bool row_ok = row < p.M;
+            const uint32_t taddr = tmem_base + buf * BN + (uint32_t(lg * 32) << 16);
+            constexpr int CW = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int c = 0; c < BN / CW; c++) {
+                const int col0 = tc.n0 + c * CW;
+                if (col0 >= p.N) break;
+                float v[CW];
+                if constexpr (CW == 32) {
+                    uint32_t r[32];
+                    tmem_ld_x32(taddr + c * CW, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+                } else {
+                    uint32_t r[16];
+                    tmem_ld_x16(taddr + c * CW, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+                }
+                if (!row_ok) continue;
+#pragma unroll
+                for (int g = 0; g < CW / 8; g++) {
+                    const int col = col0 + g * 8;
+                    if (col >= p.N) break;
+                    float o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) o[i] = v[g * 8 + i] * p.alpha;
+                    if (p.bias) {
+                        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const float2 f = unpack_bf16x2(bw[i]);
+                            o[2 * i] += f.x;
+                            o[2 * i + 1] += f.y;
+                        }
+                    }
+                    if (p.f32) {
+                        float* dst = (p.split_k > 1)
+                                         ? p.ws + size_t(tc.split) * p.ws_split_stride + size_t(row) * p.N + col
+                                         : reinterpret_cast<float*>(p.C) + size_t(row) * p.ldc + col;
+                        float4 lo = make_float4(o[0], o[1], o[2], o[3]);
+                        float4 hi = make_float4(o[4], o[5], o[6], o[7]);
+                        if (p.accumulate && p.split_k == 1) {
+                            const float4 a = *reinterpret_cast<const float4*>(dst);
+                            const float4 b = *reinterpret_cast<const float4*>(dst + 4);
+                            lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+                            hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+                        }
+                        *reinterpret_cast<float4*>(dst) = lo;
+                        *reinterpret_cast<float4*>(dst + 4) = hi;
+                    } else {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col;
+                        if (p.residual) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldc + col);
+                            const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const float2 f = unpack_bf16x2(rw[i]);
+                                o[2 * i] += f.x;
+                                o[2 * i + 1] += f.y;
+                            }
+                        }
+                        uint4 w;
+                        w.x = pack_bf16x2(o[0], o[1]);
+                        w.y = pack_bf16x2(o[2], o[3]);
+                        w.z = pack_bf16x2(o[4], o[5]);
+                        w.w = pack_bf16x2(o[6], o[7]);
+                        *reinterpret_cast<uint4*>(dst) = w;
+                    }
+                }
+            }
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[buf]);
+        }
+    }
+
+done:
+    __syncwarp();
+    if (*abort_flag) {
+        // give copies and MMAs already in flight time to land before shared memory / TMEM go away
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// Fixed-order reduction of split-K partials: out (+)= sum_s ws[s][m][n]; optional transposed store.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, long split_stride, int M, int N,
+                                     float* __restrict__ out, long ldo, int transpose, int accumulate) {
+    const long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+    if (i >= long(M) * N) return;
+    // thread order follows the OUTPUT's memory order so stores coalesce
+    int m, n;
+    if (transpose) { n = int(i / M); m = int(i - long(n) * M); }
+    else           { m = int(i / N); n = int(i - long(m) * N); }
+    float s = 0.f;
+    for (int k = 0; k < splits; k++) s += ws[k * split_stride + long(m) * N + n];
+    float* dst = transpose ? out + long(n) * ldo + m : out + long(m) * ldo + n;
+    *dst = accumulate ? *dst + s : s;
+}
+
+template <int BN>
+int launch(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int total_tiles) {
+    static bool attr_set[64] = {};
+    const int dev = ctx->device & 63;
+    if (!attr_set[dev]) {
+        TA_CUDA(ctx, cudaFuncSetAttribute(seg_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          int(Cfg<BN>::SMEM)));
+        attr_set[dev] = true;
+    }
+    const int grid = std::min(total_tiles, ctx->sm_count);
+    seg_gemm_kernel<BN><<<grid, 192, Cfg<BN>::SMEM, stream>>>(p);
+    TA_LAUNCH_CHECK(ctx, "seg_gemm_kernel");
+    return TA_OK;
+}
+
+int pick_bn(int N) {
+    if (N <= 16) return 16;
+    if (N <= 32) return 32;
+    if (N <= 64) return 64;
+    for (int bn : {256, 128}) {
+        const int padded = (N + bn - 1) / bn * bn;
+        if (double(padded - N) / N <= 0.04) return bn;
+    }
+    return 64;
+}
+
+}  // namespace
+
+int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* segs, int nseg, const GemmOut& out) {
+    if (!ctx) return TA_ERR_INVALID;
+    if (nseg < 1 || nseg > kMaxSegments) return fail(ctx, TA_ERR_INVALID, "seg_gemm: 1..6 segments");
+    if (M <= 0 || N <= 0 || (N % 8) != 0) return fail(ctx, TA_ERR_INVALID, "seg_gemm: M,N > 0 and N % 8 == 0 required");
+    if (!out.C || (out.ldc % 8) != 0) return fail(ctx, TA_ERR_INVALID, "seg_gemm: output pointer / ldc % 8");
+    if ((reinterpret_cast<uintptr_t>(out.C) & 15) || (reinterpret_cast<uintptr_t>(out.bias) & 15) ||
+        (reinterpret_cast<uintptr_t>(out.residual) & 15))
+        return fail(ctx, TA_ERR_INVALID, "seg_gemm: pointers must be 16-byte aligned");
+    if (out.split_k > 1 && (nseg != 1 || !out.f32 || out.bias || out.residual))
+        return fail(ctx, TA_ERR_INVALID, "seg_gemm: split-K needs one segment and plain fp32 output");
+    if (out.transpose_out && out.split_k <= 1)
+        return fail(ctx, TA_ERR_INVALID, "seg_gemm: transposed output only through the split-K reduce");
+    if (out.accumulate && !out.f32) return fail(ctx, TA_ERR_INVALID, "seg_gemm: accumulate needs fp32 output");
+
+    const int bn = pick_bn(N);
+    SegGemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    for (int s = 0; s < nseg; s++) {
+        const GemmSegment& g = segs[s];
+        if (!g.A || !g.B || g.K <= 0 || (g.K % 8) != 0 || (g.lda % 8) != 0 || (g.ldb % 8) != 0 ||
+            (reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15))
+            return fail(ctx, TA_ERR_INVALID, "seg_gemm: bad segment (null, K % 8, pitch % 8 or alignment)");
+        if ((g.a_mn && (M % 8)) || (!g.a_mn && false))
+            return fail(ctx, TA_ERR_INVALID, "seg_gemm: MN-major A needs M % 8 == 0");
+        int rc;
+        if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, 128, &p.tmA[s]);
+        else         rc = get_tmap_bf16(ctx, g.A, uint64_t(M), uint64_t(g.K), uint64_t(g.lda) * 2, 64, 64, &p.tmA[s]);
+        if (rc) return rc;
+        if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(bn), &p.tmB[s]);
+        else         rc = get_tmap_bf16(ctx, g.B, uint64_t(N), uint64_t(g.K), uint64_t(g.ldb) * 2, 64, 64, &p.tmB[s]);
+        if (rc) return rc;
+        p.K[s] = g.K;
+        p.a_mn[s] = g.a_mn;
+        p.b_mn[s] = g.b_mn;
+    }
+    p.nseg = nseg; p.M = M; p.N = N;
+    p.C = out.C; p.ldc = out.ldc; p.f32 = out.f32; p.accumulate = out.accumulate; p.alpha = out.alpha;
+    p.bias = out.bias; p.residual = out.residual; p.status = ctx->d_status;
+    p.split_k = 1; p.kb_per_split = 0;
+
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + bn - 1) / bn;
+    if (out.split_k > 1) {
+        const int nkb = (segs[0].K + BK - 1) / BK;
+        const int splits = std::min(out.split_k, nkb);
+        p.kb_per_split = (nkb + splits - 1) / splits;
+        p.split_k = (nkb + p.kb_per_split - 1) / p.kb_per_split;   // every split is non-empty
+        void* ws = nullptr;
+        const size_t bytes = size_t(p.split_k) * M * N * sizeof(float);
+        if (int rc = get_workspace(ctx, bytes, &ws)) return rc;
+        p.ws = static_cast<float*>(ws);
+        p.ws_split_stride = long(M) * N;
+    }
+    const int total = m_tiles * n_tiles * p.split_k;
+    int rc;
+    switch (bn) {
+        case 16:  rc = launch<16>(ctx, stream, p, total); break;
+        case 32:  rc = launch<32>(ctx, stream, p, total); break;
+        case 64:  rc = launch<64>(ctx, stream, p, total); break;
+        case 128: rc = launch<128>(ctx, stream, p, total); break;
+        default:  rc = launch<256>(ctx, stream, p, total); break;
+    }
+    if (rc) return rc;
+    if (out.split_k > 1) {
+        const long n = long(M) * N;
+        splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(
+            p.ws, p.split_k, p.ws_split_stride, M, N, static_cast<float*>(out.C), out.ldc, out.transpose_out,
+            out.accumulate);
+        TA_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
+    }
+    return TA_OK;
+}
+
+}  // namespace ta

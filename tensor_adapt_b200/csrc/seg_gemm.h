@@ -1,0 +1,47 @@
+// Segmented-K BF16 GEMM on tcgen05 / TMEM fed by TMA.
+//
+//   D[M,N] = alpha * sum_s  A_s[M,K_s] . B_s[N,K_s]^T   (+ bias[N]) (+ residual[M,N])
+//
+// Each segment names its own pair of operands, so a LoRA-augmented projection
+// y = x.W^T + (s.h).B^T is ONE launch with two segments accumulating into the same TMEM tile, and
+// the backward dX = dQ.Wq + dK.Wk + dV.Wv + dh_q.A_q + dh_k.A_k + dh_v.A_v is one launch with six.
+// Operands may be K-major (element [row][k], k contiguous) or MN-major (element [k][row], row
+// contiguous), which covers y = x.W^T (K-major W), dX = dY.W (MN-major W) and the token-contracted
+// LoRA gradients (both operands MN-major) without transposed copies.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "ctx.h"
+
+namespace ta {
+
+constexpr int kMaxSegments = 6;
+
+struct GemmSegment {
+    const __nv_bfloat16* A = nullptr;   // K-major: [M][K] ; MN-major: [K][M]
+    long lda = 0;                       // row pitch in elements
+    bool a_mn = false;
+    const __nv_bfloat16* B = nullptr;   // K-major: [N][K] ; MN-major: [K][N]
+    long ldb = 0;
+    bool b_mn = false;
+    int K = 0;
+};
+
+struct GemmOut {
+    void* C = nullptr;                  // [M][ldc]  bf16 or fp32
+    long ldc = 0;
+    bool f32 = false;                   // output element type
+    bool accumulate = false;            // fp32 only: C += result
+    float alpha = 1.f;
+    const __nv_bfloat16* bias = nullptr;      // [N] or null
+    const __nv_bfloat16* residual = nullptr;  // [M][ldc] or null (may alias C)
+    int split_k = 1;                    // >1: fp32 partials into ws[split][M][N] then a fixed-order reduce
+    bool transpose_out = false;         // split-K reduce only: write C[n][m] (C is [N][ldc])
+};
+
+// Launches on `stream`; asynchronous. Returns TA_OK or a negative error code.
+int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* segs, int nseg, const GemmOut& out);
+
+}  // namespace ta
