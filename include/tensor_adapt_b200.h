@@ -103,6 +103,72 @@ int ta_gemm_bf16(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, l
 int ta_gemm_tokens_f32(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, long lda, const void* B, long ldb,
                        float* C, long ldc, int accumulate, int transpose_out, void* stream);
 
+/* ── LoRA-augmented projection ─────────────────────────────────────────────────────────────
+ * proj_fwd + ops::add_bias + AdapterModel::apply_lora_fwd (src/base/arch/qwen2.cu:21-30,95-108;
+ * src/adapter/adapter_model.cu:96-129) as one fused product:
+ *     y[BT,out] = x.W^T (+ bias) + scale*(x.A^T).B^T (+ residual)
+ * x [BT,in], W [out,in], A [rank,in], B [out,rank] BF16 (the working copies). A/B may be NULL (no
+ * adapter); rank must then be 0, otherwise a multiple of 16. residual (may alias y) fuses the
+ * following ops::add_inplace of the residual stream (qwen2.cu:126,150). Uses context scratch. */
+int ta_lora_linear_fwd(ta_ctx* ctx, const void* x, const void* W, const void* bias, const void* A, const void* B,
+                       const void* residual, void* y, int BT, int in_dim, int out_dim, int rank, float scale,
+                       void* stream);
+/* proj_bwd_x + AdapterModel::apply_lora_bwd (qwen2.cu:32-41; adapter_model.cu:131-220):
+ *     dX[BT,in] = (accumulate_dx ? dX : 0) + dY.W + scale*(dY.B).A
+ *     gA[rank,in] += scale*(dY.B)^T.x        gB[out,rank] += scale*dY^T.(x.A^T)        (FP32)
+ * with h = x.A^T and dh = dY.B rounded to BF16 as in the reference. Uses context scratch (split-K
+ * partials reduced in a fixed order, so results are bit-identical from run to run). */
+int ta_lora_linear_bwd(ta_ctx* ctx, const void* x, const void* dY, const void* W, const void* A, const void* B, void* dX,
+                       int accumulate_dx, float* gA, float* gB, int BT, int in_dim, int out_dim, int rank, float scale,
+                       void* stream);
+
+/* ── attention ─────────────────────────────────────────────────────────────────────────────
+ * ops::sdpa_fwd / ops::sdpa_bwd (ops.hpp:52-70, src/backend/cuda/ops.cu:578-907): causal GQA
+ * attention, scale 1/sqrt(head_dim), Q/out [B*T, Hq*hd], K/V [B*T, Hkv*hd]. Instead of the
+ * reference's FP32 attn_w[B,Hq,T,T] cache only lse[B,Hq,T] (FP32, natural log) is kept, and the
+ * backward also takes the forward output. head_dim 64 or 128. delta_scratch: FP32 [B*Hq*T] or NULL
+ * (context scratch). */
+int ta_flash_attn_fwd(ta_ctx* ctx, const void* Q, const void* K, const void* V, void* out, float* lse, int B, int T,
+                      int Hq, int Hkv, int head_dim, void* stream);
+int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* K, const void* V, const void* out,
+                      const float* lse, void* dQ, void* dK, void* dV, float* delta_scratch, int B, int T, int Hq, int Hkv,
+                      int head_dim, void* stream);
+
+/* ── optimiser ─────────────────────────────────────────────────────────────────────────────
+ * ops::sum_sq_into (ops.hpp:154, ops.cu:1175-1193): *accum += sum g[i]^2, two-stage fixed-order. */
+int ta_sum_sq_into(ta_ctx* ctx, const float* g, float* accum, long n, void* stream);
+/* ops::adamw_step (ops.hpp:139-148, ops.cu:1139-1169); step is 1-based. */
+int ta_adamw_step(ta_ctx* ctx, float* master, void* working, float* m, float* v, const float* grad, long n, float lr,
+                  float beta1, float beta2, float eps, float weight_decay, int step, void* stream);
+/* compute_grad_norm + clip_gradients + AdamW::step_all (src/trainer/adapt_trainer.cu:32-70,
+ * src/trainer/adamw.cu:9-38) over ONE flat arena holding every LoRA tensor: norm = ||grad||_2; if
+ * max_norm > 0 and norm > max_norm the gradient is scaled by max_norm/(norm+1e-6); then AdamW.
+ * stats_dev (device, 2 floats) receives {norm, applied scale}; nothing is copied to the host.
+ * scale_grads_in_place != 0 also leaves the scaled gradient in `grad`, as the reference does. */
+int ta_gradnorm_clip_adamw(ta_ctx* ctx, float* master, void* working, float* m, float* v, float* grad, long n, float lr,
+                           float beta1, float beta2, float eps, float weight_decay, int step, float max_norm,
+                           float* stats_dev, int scale_grads_in_place, void* stream);
+
+/* ── Centroid Accumulator ──────────────────────────────────────────────────────────────────
+ * CentroidAccumulator::accumulate (include/tensor/centroid/centroid_accumulator.hpp:24-34,
+ * src/centroid/centroid_accumulator.cpp:23-70) with the state (acc[D], weight) kept on the device.
+ * hidden / grad_signal are BF16 [BT,D].
+ *   TA_CENTROID_INTENDED  acc[d] += h[t,d]*||g[t,:]||_2, weight += ||g[t,:]||_2 (documented formula)
+ *   TA_CENTROID_ASBUILT   what the shipped trainer computes (src/trainer/adapt_trainer.cu:210-232 hands
+ *                         accumulate() FP32 copies which it re-reads as BF16): token u/2, half u%2 for
+ *                         u < BT, gamma_u = ||g[tok, half*D/2 ..]||, acc[2m+1] += h[tok, half*D/2+m]*gamma_u */
+#define TA_CENTROID_INTENDED 0
+#define TA_CENTROID_ASBUILT  1
+int ta_centroid_accumulate(ta_ctx* ctx, int mode, const void* hidden, const void* grad_signal, int BT, int D, float* acc,
+                           float* weight, void* stream);
+/* The k-means of CentroidAccumulator::merge_and_write (centroid_accumulator.cpp:114-157) on device
+ * vectors [N,D] FP32: even-spread init, <= max_iters passes, strict '<' ties, early exit, zero
+ * vectors for empty clusters; FP32 operation order kept so centres and assignments are bit-exact
+ * with the host loop. centers [min(k,N), D] and assign [N] are device buffers; *k_out / *passes_out
+ * are host ints. Synchronises the stream once per pass (to read the "changed" flag). */
+int ta_kmeans_merge(ta_ctx* ctx, const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign,
+                    int* k_out, int* passes_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,16 @@ _PROTOS = {
     "ta_cast_bf16_to_f32": (c_int, [P, P, P, c_long, P]),
     "ta_cast_f32_to_bf16": (c_int, [P, P, P, c_long, P]),
     "ta_gemm_bf16": (c_int, [P, c_int, c_int, c_int, c_float, P, c_long, c_int, P, c_long, c_int, P, P, P, c_long, P]),
+    "ta_lora_linear_fwd": (c_int, [P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_float, P]),
+    "ta_lora_linear_bwd": (c_int, [P, P, P, P, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_float, P]),
+    "ta_flash_attn_fwd": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
+    "ta_flash_attn_bwd": (c_int, [P, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
+    "ta_sum_sq_into": (c_int, [P, P, P, c_long, P]),
+    "ta_adamw_step": (c_int, [P, P, P, P, P, P, c_long, c_float, c_float, c_float, c_float, c_float, c_int, P]),
+    "ta_gradnorm_clip_adamw": (c_int, [P, P, P, P, P, P, c_long, c_float, c_float, c_float, c_float, c_float, c_int,
+                                       c_float, P, c_int, P]),
+    "ta_centroid_accumulate": (c_int, [P, c_int, P, P, c_int, c_int, P, P, P]),
+    "ta_kmeans_merge": (c_int, [P, P, c_int, c_int, c_int, c_int, P, P, POINTER(c_int), POINTER(c_int), P]),
     "ta_gemm_tokens_f32": (c_int, [P, c_int, c_int, c_int, c_float, P, c_long, P, c_long, P, c_long, c_int, c_int, P]),
 }
 

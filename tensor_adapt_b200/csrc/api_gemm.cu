@@ -31,12 +31,7 @@ int ta_gemm_tokens_f32(ta_ctx* ctx, int M, int N, int K, float alpha, const void
     GemmOut o;
     o.C = C; o.ldc = ldc; o.alpha = alpha; o.f32 = true; o.accumulate = accumulate != 0;
     o.transpose_out = transpose_out != 0;
-    const int bn = N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : 128;
-    const int tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
-    const int nkb = (K + 63) / 64;
-    // enough CTAs to pull the token-major operand through every SM, but at least 8 k-blocks each
-    int splits = std::max(1, std::min({(2 * ctx->sm_count + tiles - 1) / tiles, (nkb + 7) / 8, 256}));
-    o.split_k = std::max(2, splits);   // the split path also provides transpose / accumulate
+    o.split_k = tokens_gemm_splits(ctx, M, N, K);
     return seg_gemm(ctx, static_cast<cudaStream_t>(stream), M, N, &s, 1, o);
 }
 

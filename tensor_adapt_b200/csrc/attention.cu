@@ -1,0 +1,706 @@
+// Causal GQA attention for sm_100a, flash style: no [T,T] matrix ever reaches HBM, only
+// LSE[B,Hq,T] is saved for the backward.  All contractions run on tcgen05 with TMEM accumulators,
+// operands arrive by TMA into 128B-swizzled shared memory.
+//
+// Layouts (the reference's, src/backend/cuda/ops.cu:440-458): Q, O, dO, dQ are [B*T, Hq*hd],
+// K, V, dK, dV are [B*T, Hkv*hd], heads interleaved in the feature dimension; hd is 64 or 128.
+//
+//   attn_fwd_kernel     CTA = (128 query rows, head, batch); S = Q.K^T and O_j = P.V per 128-key tile
+//   attn_delta_kernel   delta[b,h,t] = sum_d dO*O
+//   attn_bwd_dq_kernel  CTA = (128 query rows, head, batch); dQ accumulates in TMEM over key tiles
+//   attn_bwd_dkv_kernel CTA = (128 key rows, KV head, batch); dK, dV accumulate in TMEM over all query
+//                       tiles AND all query heads of the GQA group, so no atomics are needed
+//
+// 192 threads per CTA: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = softmax / element-wise
+// work with one thread per tile row (TMEM lane).  Every wait is bounded.
+#include <algorithm>
+#include <cmath>
+
+#include "ctx.h"
+#include "ptx.cuh"
+
+namespace ta {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct AttnParams {
+    CUtensorMap tmQ, tmK, tmV, tmdO;
+    __nv_bfloat16* out;        // fwd: O ; dq: dQ
+    __nv_bfloat16* out2;       // dkv: dK
+    __nv_bfloat16* out3;       // dkv: dV
+    float* lse;                // [B*Hq*T]
+    const float* delta;        // [B*Hq*T]
+    int B, T, Hq, Hkv;
+    float scale, scale_log2;
+    int* status;
+};
+
+// byte offset of element (row, col) of a [128][128]-element BF16 operand stored as two K-major
+// 64-column chunks of [128 rows][128 B] with the 128-byte swizzle (16-byte units XOR row%8)
+__device__ __forceinline__ uint32_t kmajor_off(int row, int col) {
+    const int chunk = col >> 6, c = col & 63;
+    return uint32_t(chunk) * 16384u + uint32_t(row) * 128u + uint32_t(((c >> 3) ^ (row & 7)) << 4) + uint32_t(c & 7) * 2u;
+}
+
+template <int HD>
+struct Tile {
+    static constexpr int NC = HD / 64;
+    static constexpr uint32_t BYTES = NC * 16384u;
+};
+
+// D[128, N] (+)= A[128, HD] . B[N=128, HD]^T, both K-major tiles of NC 64-column chunks
+template <int HD>
+__device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, bool accumulate) {
+    constexpr uint32_t idesc = umma_idesc_bf16(128, 128, false, false);
+#pragma unroll
+    for (int c = 0; c < Tile<HD>::NC; c++)
+#pragma unroll
+        for (int ki = 0; ki < 4; ki++)
+            umma_bf16(d_tmem, smem_desc_sw128(a_smem + c * 16384 + ki * 32, 16, 1024),
+                      smem_desc_sw128(b_smem + c * 16384 + ki * 32, 16, 1024), idesc, (accumulate || c || ki) ? 1u : 0u);
+}
+
+// D[128, HD] (+)= A[128, 128] . B[128 (k), HD (n)]: A K-major (two 64-column chunks), B is a
+// [128 rows][HD] tile read MN-major (n chunks 16384 B apart, 8-row groups 1024 B apart)
+template <int HD>
+__device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, bool accumulate) {
+    constexpr uint32_t idesc = umma_idesc_bf16(128, HD, false, true);
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++)
+        umma_bf16(d_tmem, smem_desc_sw128(a_smem + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                  smem_desc_sw128(b_smem + ks * 2048, 16384, 1024), idesc, (accumulate || ks) ? 1u : 0u);
+}
+
+template <int HD>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col0, int row0) {
+#pragma unroll
+    for (int c = 0; c < Tile<HD>::NC; c++) tma_load_2d(dst + c * 16384, tm, bar, col0 + 64 * c, row0);
+}
+
+#define ATT_WAIT(bar, parity, code) \
+    if (!mbar_wait((bar), (parity), abort_flag, p.status, (code))) goto done
+
+// ─────────────────────────────── forward ───────────────────────────────
+
+template <int HD>
+__global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
+    constexpr uint32_t TB = Tile<HD>::BYTES;
+    constexpr uint32_t OFF_Q = 0, OFF_K = TB, OFF_V = 3 * TB, OFF_P = 5 * TB, OFF_BAR = 5 * TB + 32768;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
+             *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 14, *o_empty = bars + 15;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = gridDim.x - 1 - blockIdx.x;   // heavy (late) query tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.Hq / p.Hkv);
+    const int n = qt + 1;                        // key tiles 0..qt
+    const int q0 = qt * 128;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+        }
+        mbar_init(p_full, 4); mbar_init(o_full, 1); mbar_init(o_empty, 4);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t TM_O = tmem + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, TB);
+            load_tile<HD>(smem + OFF_Q, &p.tmQ, q_full, h * HD, b * p.T + q0);
+            for (int j = 0; j < n; j++) {
+                const int st = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
+                ATT_WAIT(&k_empty[st], ph ^ 1u, DS_TIMEOUT_PRODUCER);
+                mbar_arrive_expect_tx(&k_full[st], TB);
+                load_tile<HD>(smem + OFF_K + st * TB, &p.tmK, &k_full[st], hk * HD, b * p.T + j * 128);
+                ATT_WAIT(&v_empty[st], ph ^ 1u, DS_TIMEOUT_PRODUCER);
+                mbar_arrive_expect_tx(&v_full[st], TB);
+                load_tile<HD>(smem + OFF_V + st * TB, &p.tmV, &v_full[st], hk * HD, b * p.T + j * 128);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t sQ = smem_u32(smem + OFF_Q), sK = smem_u32(smem + OFF_K), sV = smem_u32(smem + OFF_V),
+                           sP = smem_u32(smem + OFF_P);
+            ATT_WAIT(q_full, 0, DS_TIMEOUT_MMA);
+            for (int j = -1; j < n; j++) {
+                if (j + 1 < n) {   // scores of the next key tile, into the other S buffer
+                    const int jn = j + 1, st = jn & 1;
+                    const uint32_t ph = (jn >> 1) & 1;
+                    ATT_WAIT(&k_full[st], ph, DS_TIMEOUT_MMA);
+                    ATT_WAIT(&s_empty[st], ph ^ 1u, DS_TIMEOUT_MMA);
+                    tcgen05_fence_after_sync();
+                    mma_kk<HD>(tmem + st * 128, sQ, sK + st * TB, false);
+                    umma_commit(&k_empty[st]);
+                    umma_commit(&s_full[st]);
+                }
+                if (j >= 0) {
+                    const int st = j & 1;
+                    ATT_WAIT(&v_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
+                    ATT_WAIT(p_full, j & 1, DS_TIMEOUT_MMA);
+                    ATT_WAIT(o_empty, (j & 1) ^ 1u, DS_TIMEOUT_MMA);
+                    tcgen05_fence_after_sync();
+                    mma_kmn<HD>(TM_O, sP, sV + st * TB, false);
+                    umma_commit(&v_empty[st]);
+                    umma_commit(o_full);
+                }
+            }
+        }
+    } else {
+        const int lg = warp & 3;
+        const int row = lg * 32 + lane;
+        const int q_idx = q0 + row;
+        const uint32_t lane_addr = uint32_t(lg * 32) << 16;
+        float m = -INFINITY, l = 0.f;
+        float o[HD];
+#pragma unroll
+        for (int i = 0; i < HD; i++) o[i] = 0.f;
+        uint8_t* sP = smem + OFF_P;
+
+        for (int j = 0; j < n; j++) {
+            const int st = j & 1;
+            ATT_WAIT(&s_full[st], (j >> 1) & 1, DS_TIMEOUT_SOFTMAX);
+            tcgen05_fence_after_sync();
+            const bool diag = (j == qt);
+            const uint32_t ts = tmem + st * 128 + lane_addr;
+            float mx = m;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t r[32];
+                tmem_ld_x32(ts + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float s = __uint_as_float(r[i]) * p.scale_log2;
+                    if (diag && (j * 128 + c * 32 + i > q_idx)) s = -INFINITY;
+                    mx = fmaxf(mx, s);
+                }
+            }
+            const float alpha = exp2f(m - mx);   // m = -inf on the first tile -> 0
+            if (j > 0) {
+                ATT_WAIT(o_full, (j - 1) & 1, DS_TIMEOUT_SOFTMAX);
+                tcgen05_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < HD / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld_x32(TM_O + lane_addr + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * alpha;
+                }
+                tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(o_empty);
+            }
+            l *= alpha;
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t r[32];
+                tmem_ld_x32(ts + c * 32, r);
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float s0 = __uint_as_float(r[i]) * p.scale_log2, s1 = __uint_as_float(r[i + 1]) * p.scale_log2;
+                    float p0 = exp2f(s0 - mx), p1 = exp2f(s1 - mx);
+                    if (diag) {
+                        if (j * 128 + c * 32 + i > q_idx) p0 = 0.f;
+                        if (j * 128 + c * 32 + i + 1 > q_idx) p1 = 0.f;
+                    }
+                    sum += p0 + p1;
+                    pk[i >> 1] = pack_bf16x2(p0, p1);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; g++)
+                    *reinterpret_cast<uint4*>(sP + kmajor_off(row, c * 32 + g * 8)) =
+                        make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+            }
+            l += sum;
+            m = mx;
+            fence_proxy_async_smem();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&s_empty[st]); mbar_arrive(p_full); }
+        }
+        ATT_WAIT(o_full, (n - 1) & 1, DS_TIMEOUT_SOFTMAX);
+        tcgen05_fence_after_sync();
+        const float inv_l = 1.f / l;
+        const bool ok = q_idx < p.T;
+        __nv_bfloat16* orow = p.out + (size_t(b) * p.T + q_idx) * (size_t(p.Hq) * HD) + h * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; c++) {
+            uint32_t r[32];
+            tmem_ld_x32(TM_O + lane_addr + c * 32, r);
+            tmem_ld_wait();
+            if (ok) {
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int e = c * 32 + g * 8 + i * 2;
+                        w[i] = pack_bf16x2((o[e] + __uint_as_float(r[g * 8 + i * 2])) * inv_l,
+                                           (o[e + 1] + __uint_as_float(r[g * 8 + i * 2 + 1])) * inv_l);
+                    }
+                    *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+        if (ok) p.lse[(size_t(b) * p.Hq + h) * p.T + q_idx] = m * kLn2 + logf(l);
+    }
+done:
+    __syncwarp();
+    if (*abort_flag) for (int i = 0; i < 200; i++) __nanosleep(1000);
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) { tcgen05_fence_after_sync(); tmem_dealloc(tmem, 512); }
+}
+
+// delta[b,h,t] = sum_d dO[bt, h*hd+d] * O[bt, h*hd+d]; one warp per (token, head)
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                  float* __restrict__ delta, int B, int T, int Hq, int hd) {
+    const long wid = (blockIdx.x * long(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= long(B) * T * Hq) return;
+    const int h = int(wid % Hq);
+    const long bt = wid / Hq;
+    const uint4* a = reinterpret_cast<const uint4*>(dO + (bt * Hq + h) * hd);
+    const uint4* o = reinterpret_cast<const uint4*>(O + (bt * Hq + h) * hd);
+    float s = 0.f;
+    if (lane < hd / 8) {
+        const uint4 x = a[lane], y = o[lane];
+        const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 f = unpack_bf16x2(xw[i]), g = unpack_bf16x2(yw[i]);
+            s += f.x * g.x + f.y * g.y;
+        }
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+        const int b = int(bt / T), t = int(bt % T);
+        delta[(size_t(b) * Hq + h) * T + t] = s;
+    }
+}
+
+// ─────────────────────────────── backward: dQ ───────────────────────────────
+
+template <int HD>
+__global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
+    constexpr uint32_t TB = Tile<HD>::BYTES;
+    constexpr uint32_t OFF_Q = 0, OFF_DO = TB, OFF_K = 2 * TB, OFF_V = 4 * TB, OFF_DS = 6 * TB, OFF_BAR = 6 * TB + 32768;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t *qdo_full = bars, *kv_full = bars + 1, *kv_empty = bars + 3, *s_full = bars + 5, *s_empty = bars + 6,
+             *ds_full = bars + 7, *dq_full = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.Hq / p.Hkv);
+    const int n = qt + 1;
+    const int q0 = qt * 128;
+
+    if (threadIdx.x == 0) {
+        mbar_init(qdo_full, 1);
+        for (int i = 0; i < 2; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        mbar_init(s_full, 1); mbar_init(s_empty, 4); mbar_init(ds_full, 4); mbar_init(dq_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t TM_S = tmem, TM_DP = tmem + 128, TM_DQ = tmem + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(qdo_full, 2 * TB);
+            load_tile<HD>(smem + OFF_Q, &p.tmQ, qdo_full, h * HD, b * p.T + q0);
+            load_tile<HD>(smem + OFF_DO, &p.tmdO, qdo_full, h * HD, b * p.T + q0);
+            for (int j = 0; j < n; j++) {
+                const int st = j & 1;
+                ATT_WAIT(&kv_empty[st], ((j >> 1) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
+                mbar_arrive_expect_tx(&kv_full[st], 2 * TB);
+                load_tile<HD>(smem + OFF_K + st * TB, &p.tmK, &kv_full[st], hk * HD, b * p.T + j * 128);
+                load_tile<HD>(smem + OFF_V + st * TB, &p.tmV, &kv_full[st], hk * HD, b * p.T + j * 128);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t sQ = smem_u32(smem + OFF_Q), sDO = smem_u32(smem + OFF_DO), sK = smem_u32(smem + OFF_K),
+                           sV = smem_u32(smem + OFF_V), sDS = smem_u32(smem + OFF_DS);
+            ATT_WAIT(qdo_full, 0, DS_TIMEOUT_MMA);
+            for (int j = 0; j < n; j++) {
+                const int st = j & 1;
+                ATT_WAIT(&kv_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
+                ATT_WAIT(s_empty, (j & 1) ^ 1u, DS_TIMEOUT_MMA);
+                tcgen05_fence_after_sync();
+                mma_kk<HD>(TM_S, sQ, sK + st * TB, false);
+                mma_kk<HD>(TM_DP, sDO, sV + st * TB, false);
+                umma_commit(s_full);
+                ATT_WAIT(ds_full, j & 1, DS_TIMEOUT_MMA);
+                tcgen05_fence_after_sync();
+                mma_kmn<HD>(TM_DQ, sDS, sK + st * TB, j > 0);
+                umma_commit(&kv_empty[st]);
+            }
+            umma_commit(dq_full);
+        }
+    } else {
+        const int lg = warp & 3;
+        const int row = lg * 32 + lane;
+        const int q_idx = q0 + row;
+        const bool ok = q_idx < p.T;
+        const uint32_t lane_addr = uint32_t(lg * 32) << 16;
+        const size_t stat = (size_t(b) * p.Hq + h) * p.T + q_idx;
+        const float lse2 = ok ? p.lse[stat] * kLog2e : INFINITY;
+        const float dlt = ok ? p.delta[stat] : 0.f;
+        uint8_t* sDS = smem + OFF_DS;
+        for (int j = 0; j < n; j++) {
+            ATT_WAIT(s_full, j & 1, DS_TIMEOUT_SOFTMAX);
+            tcgen05_fence_after_sync();
+            const bool diag = (j == qt);
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t rs[32], rp[32];
+                tmem_ld_x32(TM_S + lane_addr + c * 32, rs);
+                tmem_ld_x32(TM_DP + lane_addr + c * 32, rp);
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2);
+                    float p1 = exp2f(__uint_as_float(rs[i + 1]) * p.scale_log2 - lse2);
+                    if (diag) {
+                        if (j * 128 + c * 32 + i > q_idx) p0 = 0.f;
+                        if (j * 128 + c * 32 + i + 1 > q_idx) p1 = 0.f;
+                    }
+                    pk[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(rp[i]) - dlt) * p.scale,
+                                             p1 * (__uint_as_float(rp[i + 1]) - dlt) * p.scale);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; g++)
+                    *reinterpret_cast<uint4*>(sDS + kmajor_off(row, c * 32 + g * 8)) =
+                        make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+            }
+            fence_proxy_async_smem();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(s_empty); mbar_arrive(ds_full); }
+        }
+        ATT_WAIT(dq_full, 0, DS_TIMEOUT_SOFTMAX);
+        tcgen05_fence_after_sync();
+        __nv_bfloat16* orow = p.out + (size_t(b) * p.T + q_idx) * (size_t(p.Hq) * HD) + h * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; c++) {
+            uint32_t r[32];
+            tmem_ld_x32(TM_DQ + lane_addr + c * 32, r);
+            tmem_ld_wait();
+            if (ok) {
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        w[i] = pack_bf16x2(__uint_as_float(r[g * 8 + i * 2]), __uint_as_float(r[g * 8 + i * 2 + 1]));
+                    *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+done:
+    __syncwarp();
+    if (*abort_flag) for (int i = 0; i < 200; i++) __nanosleep(1000);
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) { tcgen05_fence_after_sync(); tmem_dealloc(tmem, 512); }
+}
+
+// ─────────────────────────────── backward: dK, dV ───────────────────────────────
+
+template <int HD>
+__global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
+    constexpr uint32_t TB = Tile<HD>::BYTES;
+    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 3 * TB, OFF_PT = 4 * TB, OFF_DST = 4 * TB + 32768,
+                       OFF_STAT = 4 * TB + 65536, OFF_BAR = OFF_STAT + 2048;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 2, *s_full = bars + 3, *s_empty = bars + 4,
+             *p_full = bars + 5, *acc_full = bars + 6, *stat_full = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* stat = reinterpret_cast<float*>(smem + OFF_STAT);   // [2 buffers][lse2 128 | delta 128]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kt = blockIdx.x;   // key tile; tile 0 has the most work and starts first
+    const int hk = blockIdx.y, b = blockIdx.z;
+    const int G = p.Hq / p.Hkv;
+    const int nq = (p.T + 127) / 128;
+    const int per_head = nq - kt;
+    const int iters = G * per_head;
+    const int kv0 = kt * 128;
+
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1);
+        mbar_init(s_full, 1); mbar_init(s_empty, 4); mbar_init(p_full, 4); mbar_init(acc_full, 1);
+        mbar_init(stat_full, 128);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t TM_ST = tmem, TM_DPT = tmem + 128, TM_DV = tmem + 256, TM_DK = tmem + 256 + HD;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(kv_full, 2 * TB);
+            load_tile<HD>(smem + OFF_K, &p.tmK, kv_full, hk * HD, b * p.T + kv0);
+            load_tile<HD>(smem + OFF_V, &p.tmV, kv_full, hk * HD, b * p.T + kv0);
+            for (int it = 0; it < iters; it++) {
+                const int h = hk * G + it / per_head, qi = kt + it % per_head;
+                ATT_WAIT(qdo_empty, (it & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
+                mbar_arrive_expect_tx(qdo_full, 2 * TB);
+                load_tile<HD>(smem + OFF_Q, &p.tmQ, qdo_full, h * HD, b * p.T + qi * 128);
+                load_tile<HD>(smem + OFF_DO, &p.tmdO, qdo_full, h * HD, b * p.T + qi * 128);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t sK = smem_u32(smem + OFF_K), sV = smem_u32(smem + OFF_V), sQ = smem_u32(smem + OFF_Q),
+                           sDO = smem_u32(smem + OFF_DO), sPT = smem_u32(smem + OFF_PT), sDST = smem_u32(smem + OFF_DST);
+            ATT_WAIT(kv_full, 0, DS_TIMEOUT_MMA);
+            for (int it = 0; it < iters; it++) {
+                ATT_WAIT(qdo_full, it & 1, DS_TIMEOUT_MMA);
+                ATT_WAIT(s_empty, (it & 1) ^ 1u, DS_TIMEOUT_MMA);
+                tcgen05_fence_after_sync();
+                mma_kk<HD>(TM_ST, sK, sQ, false);     // S^T  = K . Q^T
+                mma_kk<HD>(TM_DPT, sV, sDO, false);   // dP^T = V . dO^T
+                umma_commit(s_full);
+                ATT_WAIT(p_full, it & 1, DS_TIMEOUT_MMA);
+                tcgen05_fence_after_sync();
+                mma_kmn<HD>(TM_DV, sPT, sDO, it > 0);   // dV += P^T . dO
+                mma_kmn<HD>(TM_DK, sDST, sQ, it > 0);   // dK += dS^T . Q
+                umma_commit(qdo_empty);
+            }
+            umma_commit(acc_full);
+        }
+    } else {
+        const int lg = warp & 3;
+        const int row = lg * 32 + lane;     // key row of this thread
+        const int tid = threadIdx.x - 64;   // 0..127 among the compute threads
+        const int kv_idx = kv0 + row;
+        const uint32_t lane_addr = uint32_t(lg * 32) << 16;
+        uint8_t* sPT = smem + OFF_PT;
+        uint8_t* sDST = smem + OFF_DST;
+        for (int it = 0; it < iters; it++) {
+            const int h = hk * G + it / per_head, qi = kt + it % per_head;
+            float* lse2 = stat + (it & 1) * 256;
+            float* dlt = lse2 + 128;
+            {
+                const int q = qi * 128 + tid;
+                const bool okq = q < p.T;
+                const size_t si = (size_t(b) * p.Hq + h) * p.T + q;
+                lse2[tid] = okq ? p.lse[si] * kLog2e : INFINITY;   // +inf -> probability 0 for padded queries
+                dlt[tid] = okq ? p.delta[si] : 0.f;
+            }
+            mbar_arrive(stat_full);   // all 128 rows of lse / delta are in shared memory after this phase
+            ATT_WAIT(stat_full, it & 1, DS_TIMEOUT_SOFTMAX);
+            ATT_WAIT(s_full, it & 1, DS_TIMEOUT_SOFTMAX);
+            tcgen05_fence_after_sync();
+            const bool diag = (qi == kt);
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t rs[32], rp[32];
+                tmem_ld_x32(TM_ST + lane_addr + c * 32, rs);
+                tmem_ld_x32(TM_DPT + lane_addr + c * 32, rp);
+                tmem_ld_wait();
+                uint32_t pk[16], dk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int col = c * 32 + i;
+                    float p0 = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2[col]);
+                    float p1 = exp2f(__uint_as_float(rs[i + 1]) * p.scale_log2 - lse2[col + 1]);
+                    if (diag) {
+                        if (kv_idx > qi * 128 + col) p0 = 0.f;
+                        if (kv_idx > qi * 128 + col + 1) p1 = 0.f;
+                    }
+                    pk[i >> 1] = pack_bf16x2(p0, p1);
+                    dk[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(rp[i]) - dlt[col]) * p.scale,
+                                             p1 * (__uint_as_float(rp[i + 1]) - dlt[col + 1]) * p.scale);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const uint32_t off = kmajor_off(row, c * 32 + g * 8);
+                    *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                    *reinterpret_cast<uint4*>(sDST + off) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
+                }
+            }
+            fence_proxy_async_smem();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(s_empty); mbar_arrive(p_full); }
+        }
+        ATT_WAIT(acc_full, 0, DS_TIMEOUT_SOFTMAX);
+        tcgen05_fence_after_sync();
+        const bool ok = kv_idx < p.T;
+        const size_t ro = (size_t(b) * p.T + kv_idx) * (size_t(p.Hkv) * HD) + hk * HD;
+#pragma unroll
+        for (int which = 0; which < 2; which++) {
+            __nv_bfloat16* orow = (which == 0 ? p.out3 : p.out2) + ro;
+            const uint32_t ta = (which == 0 ? TM_DV : TM_DK) + lane_addr;
+#pragma unroll
+            for (int c = 0; c < HD / 32; c++) {
+                uint32_t r[32];
+                tmem_ld_x32(ta + c * 32, r);
+                tmem_ld_wait();
+                if (ok) {
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            w[i] = pack_bf16x2(__uint_as_float(r[g * 8 + i * 2]), __uint_as_float(r[g * 8 + i * 2 + 1]));
+                        *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+done:
+    __syncwarp();
+    if (*abort_flag) for (int i = 0; i < 200; i++) __nanosleep(1000);
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) { tcgen05_fence_after_sync(); tmem_dealloc(tmem, 512); }
+}
+
+template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 32768 + 256 + 1024; }
+template <int HD> constexpr size_t dq_smem()  { return 6 * Tile<HD>::BYTES + 32768 + 256 + 1024; }
+template <int HD> constexpr size_t dkv_smem() { return 4 * Tile<HD>::BYTES + 65536 + 2048 + 256 + 1024; }
+
+int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const void* V, const void* dO, int B, int T,
+              int Hq, int Hkv, int hd) {
+    const uint64_t rows = uint64_t(B) * T;
+    int rc;
+    if ((rc = get_tmap_bf16(ctx, Q, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 128, &p.tmQ))) return rc;
+    if ((rc = get_tmap_bf16(ctx, K, uint64_t(Hkv) * hd, rows, uint64_t(Hkv) * hd * 2, 64, 128, &p.tmK))) return rc;
+    if ((rc = get_tmap_bf16(ctx, V, uint64_t(Hkv) * hd, rows, uint64_t(Hkv) * hd * 2, 64, 128, &p.tmV))) return rc;
+    if (dO && (rc = get_tmap_bf16(ctx, dO, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 128, &p.tmdO))) return rc;
+    return TA_OK;
+}
+
+int check_shape(ta_ctx* ctx, int B, int T, int Hq, int Hkv, int hd) {
+    if (B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0)
+        return fail(ctx, TA_ERR_INVALID, "attention: bad B/T/heads (Hq must be a multiple of Hkv)");
+    if (hd != 64 && hd != 128) return fail(ctx, TA_ERR_UNSUPPORTED, "attention: head_dim must be 64 or 128");
+    return TA_OK;
+}
+
+template <typename K>
+int set_smem(ta_ctx* ctx, K kernel, size_t bytes) {
+    TA_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
+    return TA_OK;
+}
+
+}  // namespace
+}  // namespace ta
+
+using namespace ta;
+
+extern "C" {
+
+int ta_flash_attn_fwd(ta_ctx* ctx, const void* Q, const void* K, const void* V, void* out, float* lse, int B, int T,
+                      int Hq, int Hkv, int head_dim, void* stream) {
+    if (!ctx || !Q || !K || !V || !out || !lse) return fail(ctx, TA_ERR_INVALID, "flash_attn_fwd: null argument");
+    if (int rc = check_shape(ctx, B, T, Hq, Hkv, head_dim)) return rc;
+    AttnParams p{};
+    if (int rc = make_maps(ctx, p, Q, K, V, nullptr, B, T, Hq, Hkv, head_dim)) return rc;
+    p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse;
+    p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+    p.scale = 1.f / std::sqrt(float(head_dim)); p.scale_log2 = p.scale * kLog2e; p.status = ctx->d_status;
+    const dim3 grid((T + 127) / 128, Hq, B);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (head_dim == 128) {
+        if (int rc = set_smem(ctx, attn_fwd_kernel<128>, fwd_smem<128>())) return rc;
+        attn_fwd_kernel<128><<<grid, 192, fwd_smem<128>(), s>>>(p);
+    } else {
+        if (int rc = set_smem(ctx, attn_fwd_kernel<64>, fwd_smem<64>())) return rc;
+        attn_fwd_kernel<64><<<grid, 192, fwd_smem<64>(), s>>>(p);
+    }
+    TA_LAUNCH_CHECK(ctx, "attn_fwd_kernel");
+    return TA_OK;
+}
+
+int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* K, const void* V, const void* out,
+                      const float* lse, void* dQ, void* dK, void* dV, float* delta_scratch, int B, int T, int Hq, int Hkv,
+                      int head_dim, void* stream) {
+    if (!ctx || !dout || !Q || !K || !V || !out || !lse || !dQ || !dK || !dV)
+        return fail(ctx, TA_ERR_INVALID, "flash_attn_bwd: null argument");
+    if (int rc = check_shape(ctx, B, T, Hq, Hkv, head_dim)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* delta = delta_scratch;
+    if (!delta) {
+        void* ws = nullptr;
+        if (int rc = get_workspace(ctx, size_t(B) * Hq * T * sizeof(float), &ws)) return rc;
+        delta = static_cast<float*>(ws);
+    }
+    const long warps = long(B) * T * Hq;
+    attn_delta_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(out), delta, B, T, Hq, head_dim);
+    TA_LAUNCH_CHECK(ctx, "attn_delta_kernel");
+
+    AttnParams p{};
+    if (int rc = make_maps(ctx, p, Q, K, V, dout, B, T, Hq, Hkv, head_dim)) return rc;
+    p.lse = const_cast<float*>(lse); p.delta = delta;
+    p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+    p.scale = 1.f / std::sqrt(float(head_dim)); p.scale_log2 = p.scale * kLog2e; p.status = ctx->d_status;
+    p.out = static_cast<__nv_bfloat16*>(dQ);
+    p.out2 = static_cast<__nv_bfloat16*>(dK);
+    p.out3 = static_cast<__nv_bfloat16*>(dV);
+    const int nt = (T + 127) / 128;
+    if (head_dim == 128) {
+        if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<128>, dkv_smem<128>())) return rc;
+        attn_bwd_dkv_kernel<128><<<dim3(nt, Hkv, B), 192, dkv_smem<128>(), s>>>(p);
+        TA_LAUNCH_CHECK(ctx, "attn_bwd_dkv_kernel");
+        if (int rc = set_smem(ctx, attn_bwd_dq_kernel<128>, dq_smem<128>())) return rc;
+        attn_bwd_dq_kernel<128><<<dim3(nt, Hq, B), 192, dq_smem<128>(), s>>>(p);
+    } else {
+        if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<64>, dkv_smem<64>())) return rc;
+        attn_bwd_dkv_kernel<64><<<dim3(nt, Hkv, B), 192, dkv_smem<64>(), s>>>(p);
+        TA_LAUNCH_CHECK(ctx, "attn_bwd_dkv_kernel");
+        if (int rc = set_smem(ctx, attn_bwd_dq_kernel<64>, dq_smem<64>())) return rc;
+        attn_bwd_dq_kernel<64><<<dim3(nt, Hq, B), 192, dq_smem<64>(), s>>>(p);
+    }
+    TA_LAUNCH_CHECK(ctx, "attn_bwd_dq_kernel");
+    return TA_OK;
+}
+
+}  // extern "C"

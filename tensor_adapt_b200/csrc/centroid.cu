@@ -1,0 +1,265 @@
+// Centroid Accumulator on the device: per-token gradient-norm-weighted sum of hidden states
+// (C = sum_t h_t * ||g_t||), and the k-means merge of snapshot vectors.
+//
+// Accumulation is HBM-bound: it reads h[BT,D] and g[BT,D] once (2*BT*D*2 bytes) and replaces the
+// reference's per-layer round trip of four [BT,D] FP32 copies over PCIe plus a scalar CPU loop.
+// Two modes:
+//   TA_CENTROID_INTENDED  acc[d] += h[t,d]*||g[t,:]||, weight += ||g[t,:]||   (the documented formula)
+//   TA_CENTROID_ASBUILT   what the shipped trainer computes after it re-reads FP32 buffers through a
+//                         BF16 pointer: pseudo-row u = 0..BT-1 covers token u/2, half u%2 of the row;
+//                         gamma_u = ||g[tok, half*D/2 : (half+1)*D/2]||, acc[2m+1] += h[tok, half*D/2+m]*gamma_u.
+// Both use a two-stage, fixed-order reduction (bit-identical from run to run).
+//
+// The k-means kernels keep the reference's FP32 operation order (no FMA contraction, sequential sums)
+// so cluster assignments and centres are bit-exact against the CPU implementation.
+#include <algorithm>
+
+#include "ctx.h"
+#include "ptx.cuh"
+
+namespace ta {
+namespace {
+
+constexpr int kRows = 32;      // token rows per CTA
+constexpr int kThreads = 256;
+constexpr int kColVec = 4;     // 16-byte column vectors per thread: D <= 256*4*8 = 8192
+
+__device__ __forceinline__ void unpack8c(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 t = unpack_bf16x2(w[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+// partial[cta][0..D) = sum over the CTA's rows of h[row][j] * gamma(row, half(j));  partial_w[cta] = sum gamma
+__global__ void __launch_bounds__(kThreads) centroid_partial_kernel(const __nv_bfloat16* __restrict__ h,
+                                                                    const __nv_bfloat16* __restrict__ g, int rows,
+                                                                    int pseudo_rows, int D, int asbuilt,
+                                                                    float* __restrict__ partial,
+                                                                    float* __restrict__ partial_w) {
+    __shared__ float gam[kRows][2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r0 = blockIdx.x * kRows;
+    const int nvec = D / 8, half_vec = nvec / 2;
+    // phase A: one warp per row computes the row's gradient norm(s)
+    for (int rl = warp; rl < kRows; rl += kThreads / 32) {
+        const int row = r0 + rl;
+        float s0 = 0.f, s1 = 0.f;
+        if (row < rows) {
+            const uint4* gr = reinterpret_cast<const uint4*>(g + size_t(row) * D);
+            for (int i = lane; i < nvec; i += 32) {
+                float f[8];
+                unpack8c(gr[i], f);
+                float s = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; e++) s += f[e] * f[e];
+                if (asbuilt && i >= half_vec) s1 += s; else s0 += s;
+            }
+        }
+        s0 = warp_sum(s0);
+        s1 = warp_sum(s1);
+        if (lane == 0) {
+            if (!asbuilt) {
+                gam[rl][0] = gam[rl][1] = sqrtf(s0);
+            } else {
+                // pseudo-rows 2*row and 2*row+1 exist only while they are < pseudo_rows
+                gam[rl][0] = (2 * row < pseudo_rows) ? sqrtf(s0) : 0.f;
+                gam[rl][1] = (2 * row + 1 < pseudo_rows) ? sqrtf(s1) : 0.f;
+            }
+        }
+    }
+    __syncthreads();
+    // phase B: column sums, coalesced 16-byte loads along the row
+    float acc[kColVec][8];
+#pragma unroll
+    for (int j = 0; j < kColVec; j++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[j][e] = 0.f;
+    const int nr = min(kRows, rows - r0);
+    for (int rl = 0; rl < nr; rl++) {
+        const uint4* hr = reinterpret_cast<const uint4*>(h + size_t(r0 + rl) * D);
+        const float g0 = gam[rl][0], g1 = gam[rl][1];
+#pragma unroll
+        for (int j = 0; j < kColVec; j++) {
+            const int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                float f[8];
+                unpack8c(hr[i], f);
+                const float gm = (asbuilt && i >= half_vec) ? g1 : g0;
+#pragma unroll
+                for (int e = 0; e < 8; e++) acc[j][e] += f[e] * gm;
+            }
+        }
+    }
+    float* out = partial + size_t(blockIdx.x) * D;
+#pragma unroll
+    for (int j = 0; j < kColVec; j++) {
+        const int i = threadIdx.x + j * kThreads;
+        if (i < nvec) {
+            *reinterpret_cast<float4*>(out + i * 8) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+            *reinterpret_cast<float4*>(out + i * 8 + 4) = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+        }
+    }
+    if (threadIdx.x == 0) {
+        float w = 0.f;
+        for (int rl = 0; rl < nr; rl++) w += asbuilt ? gam[rl][0] + gam[rl][1] : gam[rl][0];
+        partial_w[blockIdx.x] = w;
+    }
+}
+
+__global__ void centroid_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ partial_w,
+                                       int nblocks, int D, int asbuilt, float* __restrict__ acc,
+                                       float* __restrict__ weight) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d < D) {
+        float s = 0.f;
+        if (!asbuilt) {
+            for (int b = 0; b < nblocks; b++) s += partial[size_t(b) * D + d];
+            acc[d] += s;
+        } else if (d & 1) {
+            const int m = d >> 1;
+            for (int b = 0; b < nblocks; b++) s += partial[size_t(b) * D + m] + partial[size_t(b) * D + D / 2 + m];
+            acc[d] += s;
+        }
+    }
+    if (d == 0) {
+        float w = 0.f;
+        for (int b = 0; b < nblocks; b++) w += partial_w[b];
+        *weight += w;
+    }
+}
+
+// ── k-means (bit-exact with the sequential FP32 host loop) ──────────────────
+
+__global__ void kmeans_init_kernel(const float* __restrict__ vec, int N, int D, int k, float* __restrict__ centers,
+                                   int* __restrict__ assign) {
+    const long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+    if (i < long(k) * D) {
+        const int ki = int(i / D), d = int(i - long(ki) * D);
+        centers[i] = vec[size_t((long(ki) * N) / k) * D + d];
+    }
+    if (i < N) assign[i] = 0;
+}
+
+// one thread per (vector, centre): d = (((0 + v0*v0) + v1*v1) + ...) with separately rounded mul and add
+__global__ void kmeans_dist_kernel(const float* __restrict__ vec, const float* __restrict__ centers, int N, int D, int k,
+                                   float* __restrict__ dist) {
+    const long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+    if (i >= long(N) * k) return;
+    const int n = int(i / k), ki = int(i - long(n) * k);
+    const float* x = vec + size_t(n) * D;
+    const float* c = centers + size_t(ki) * D;
+    float d = 0.f;
+    for (int j = 0; j < D; j++) {
+        const float v = __fsub_rn(x[j], c[j]);
+        d = __fadd_rn(d, __fmul_rn(v, v));
+    }
+    dist[i] = d;
+}
+
+__global__ void kmeans_assign_kernel(const float* __restrict__ dist, int N, int k, int* __restrict__ assign,
+                                     int* __restrict__ changed) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float best = 1e38f;
+    int bk = 0;
+    for (int ki = 0; ki < k; ki++) {
+        const float d = dist[size_t(n) * k + ki];
+        if (d < best) { best = d; bk = ki; }   // strict '<': the lowest index wins ties
+    }
+    if (assign[n] != bk) {
+        assign[n] = bk;
+        atomicExch(changed, 1);
+    }
+}
+
+// one thread per (centre, coordinate): sequential sum over the members in vector order, then c /= count
+__global__ void kmeans_update_kernel(const float* __restrict__ vec, const int* __restrict__ assign, int N, int D, int k,
+                                     float* __restrict__ centers) {
+    const long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+    if (i >= long(k) * D) return;
+    const int ki = int(i / D), d = int(i - long(ki) * D);
+    float c = 0.f;
+    int count = 0;
+    for (int n = 0; n < N; n++) {
+        if (assign[n] == ki) {
+            c = __fadd_rn(c, vec[size_t(n) * D + d]);
+            count++;
+        }
+    }
+    centers[i] = count > 0 ? __fdiv_rn(c, float(count)) : 0.f;
+}
+
+}  // namespace
+}  // namespace ta
+
+using namespace ta;
+
+extern "C" {
+
+int ta_centroid_accumulate(ta_ctx* ctx, int mode, const void* hidden, const void* grad_signal, int BT, int D, float* acc,
+                           float* weight, void* stream) {
+    if (!ctx || !hidden || !grad_signal || !acc || !weight || BT < 0 || D <= 0)
+        return fail(ctx, TA_ERR_INVALID, "centroid_accumulate: null argument or bad size");
+    if (mode != TA_CENTROID_INTENDED && mode != TA_CENTROID_ASBUILT)
+        return fail(ctx, TA_ERR_INVALID, "centroid_accumulate: unknown mode");
+    const int asbuilt = mode == TA_CENTROID_ASBUILT;
+    if (D % (asbuilt ? 16 : 8) != 0 || D > kThreads * kColVec * 8)
+        return fail(ctx, TA_ERR_INVALID, "centroid_accumulate: D must be a multiple of 8 (16 as-built) and <= 8192");
+    if ((reinterpret_cast<uintptr_t>(hidden) & 15) || (reinterpret_cast<uintptr_t>(grad_signal) & 15))
+        return fail(ctx, TA_ERR_INVALID, "centroid_accumulate: pointers must be 16-byte aligned");
+    if (BT == 0) return TA_OK;
+    // as-built reads only the first BT*D BF16 elements of the FP32 buffers = tokens 0 .. ceil(BT/2)-1
+    const int rows = asbuilt ? (BT + 1) / 2 : BT;
+    const int blocks = (rows + kRows - 1) / kRows;
+    void* ws = nullptr;
+    if (int rc = get_workspace(ctx, size_t(blocks) * (D + 1) * sizeof(float), &ws)) return rc;
+    float* partial = static_cast<float*>(ws);
+    float* partial_w = partial + size_t(blocks) * D;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    centroid_partial_kernel<<<blocks, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(hidden),
+                                                        static_cast<const __nv_bfloat16*>(grad_signal), rows, BT, D,
+                                                        asbuilt, partial, partial_w);
+    TA_LAUNCH_CHECK(ctx, "centroid_partial_kernel");
+    centroid_reduce_kernel<<<(D + 255) / 256, 256, 0, s>>>(partial, partial_w, blocks, D, asbuilt, acc, weight);
+    TA_LAUNCH_CHECK(ctx, "centroid_reduce_kernel");
+    return TA_OK;
+}
+
+int ta_kmeans_merge(ta_ctx* ctx, const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign,
+                    int* k_out, int* passes_out, void* stream) {
+    if (!ctx || !vectors || !centers || !assign || N <= 0 || D <= 0 || k <= 0 || max_iters < 0)
+        return fail(ctx, TA_ERR_INVALID, "kmeans_merge: null argument or bad size");
+    k = std::min(k, N);
+    if (k_out) *k_out = k;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    void* ws = nullptr;
+    if (int rc = get_workspace(ctx, size_t(N) * k * sizeof(float) + 256, &ws)) return rc;
+    int* changed = static_cast<int*>(ws);
+    float* dist = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
+    const long ninit = std::max<long>(long(k) * D, N);
+    kmeans_init_kernel<<<unsigned((ninit + 255) / 256), 256, 0, s>>>(vectors, N, D, k, centers, assign);
+    TA_LAUNCH_CHECK(ctx, "kmeans_init_kernel");
+    int passes = 0;
+    for (int it = 0; it < max_iters; it++) {
+        passes++;
+        TA_CUDA(ctx, cudaMemsetAsync(changed, 0, sizeof(int), s));
+        kmeans_dist_kernel<<<unsigned((long(N) * k + 127) / 128), 128, 0, s>>>(vectors, centers, N, D, k, dist);
+        TA_LAUNCH_CHECK(ctx, "kmeans_dist_kernel");
+        kmeans_assign_kernel<<<(N + 127) / 128, 128, 0, s>>>(dist, N, k, assign, changed);
+        TA_LAUNCH_CHECK(ctx, "kmeans_assign_kernel");
+        int h = 0;
+        TA_CUDA(ctx, cudaMemcpyAsync(&h, changed, sizeof(int), cudaMemcpyDeviceToHost, s));
+        TA_CUDA(ctx, cudaStreamSynchronize(s));
+        if (!h) break;
+        kmeans_update_kernel<<<unsigned((long(k) * D + 127) / 128), 128, 0, s>>>(vectors, assign, N, D, k, centers);
+        TA_LAUNCH_CHECK(ctx, "kmeans_update_kernel");
+    }
+    if (passes_out) *passes_out = passes;
+    return TA_OK;
+}
+
+}  // extern "C"

@@ -244,12 +244,12 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
                         }
                     }
                     if (p.f32) {
-                        float* dst = (p.split_k > 1)
+                        float* dst = p.ws
                                          ? p.ws + size_t(tc.split) * p.ws_split_stride + size_t(row) * p.N + col
                                          : reinterpret_cast<float*>(p.C) + size_t(row) * p.ldc + col;
                         float4 lo = make_float4(o[0], o[1], o[2], o[3]);
                         float4 hi = make_float4(o[4], o[5], o[6], o[7]);
-                        if (p.accumulate && p.split_k == 1) {
+                        if (p.accumulate && !p.ws) {
                             const float4 a = *reinterpret_cast<const float4*>(dst);
                             const float4 b = *reinterpret_cast<const float4*>(dst + 4);
                             lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
@@ -341,6 +341,18 @@ int pick_bn(int N) {
 
 }  // namespace
 
+int tokens_gemm_splits(const ta_ctx* ctx, int M, int N, int K) {
+    const int bn = pick_bn(N);
+    const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const int nkb = (K + BK - 1) / BK;
+    // enough CTAs to pull the token-major operands through every SM, but at least 8 k-blocks each
+    const int want = std::min({(2 * ctx->sm_count + tiles - 1) / tiles, (nkb + 7) / 8, 256});
+    return std::max(2, want);   // >= 2 selects the partial + fixed-order reduce path (transpose / accumulate)
+}
+size_t tokens_gemm_ws_bytes(const ta_ctx* ctx, int M, int N, int K) {
+    return size_t(tokens_gemm_splits(ctx, M, N, K)) * M * N * sizeof(float);
+}
+
 int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* segs, int nseg, const GemmOut& out) {
     if (!ctx) return TA_ERR_INVALID;
     if (nseg < 1 || nseg > kMaxSegments) return fail(ctx, TA_ERR_INVALID, "seg_gemm: 1..6 segments");
@@ -389,7 +401,12 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
         p.split_k = (nkb + p.kb_per_split - 1) / p.kb_per_split;   // every split is non-empty
         void* ws = nullptr;
         const size_t bytes = size_t(p.split_k) * M * N * sizeof(float);
-        if (int rc = get_workspace(ctx, bytes, &ws)) return rc;
+        if (out.split_ws) {
+            if (out.split_ws_bytes < bytes) return fail(ctx, TA_ERR_NOMEM, "seg_gemm: split-K scratch too small");
+            ws = out.split_ws;
+        } else if (int rc = get_workspace(ctx, bytes, &ws)) {
+            return rc;
+        }
         p.ws = static_cast<float*>(ws);
         p.ws_split_stride = long(M) * N;
     }

@@ -39,7 +39,14 @@ struct GemmOut {
     const __nv_bfloat16* residual = nullptr;  // [M][ldc] or null (may alias C)
     int split_k = 1;                    // >1: fp32 partials into ws[split][M][N] then a fixed-order reduce
     bool transpose_out = false;         // split-K reduce only: write C[n][m] (C is [N][ldc])
+    float* split_ws = nullptr;          // split-K partials go here instead of the context workspace
+    size_t split_ws_bytes = 0;
 };
+
+// Split count the token-contracted gradient GEMM (M x N output, K tokens) should use, and the bytes
+// of partials that many splits need.
+int tokens_gemm_splits(const ta_ctx* ctx, int M, int N, int K);
+size_t tokens_gemm_ws_bytes(const ta_ctx* ctx, int M, int N, int K);
 
 // Launches on `stream`; asynchronous. Returns TA_OK or a negative error code.
 int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* segs, int nseg, const GemmOut& out);
