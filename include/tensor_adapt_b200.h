@@ -169,6 +169,117 @@ int ta_centroid_accumulate(ta_ctx* ctx, int mode, const void* hidden, const void
 int ta_kmeans_merge(ta_ctx* ctx, const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign,
                     int* k_out, int* passes_out, void* stream);
 
+/* ── model / adapter / trainer ─────────────────────────────────────────────────────────────
+ * The trainer object stands where the reference has FrozenBase + AdapterModel + AdamW +
+ * CentroidAccumulator + AdaptTrainer::Impl (include/tensor/base/frozen_base.hpp:15-56,
+ * include/tensor/adapter/adapter_model.hpp:26-95, include/tensor/trainer/adapt_trainer.hpp:18-78,
+ * src/trainer/adapt_trainer.cu:96-277).  All device memory is allocated once at creation. */
+typedef struct ta_model_config {      /* BaseConfig, frozen_base.hpp:15-29 */
+    int vocab, hidden, layers, q_heads, kv_heads, head_dim, intermediate;
+    float rms_eps, rope_theta;
+    int tie_embeddings;
+} ta_model_config;
+
+#define TA_TARGET_Q    1
+#define TA_TARGET_K    2
+#define TA_TARGET_V    4
+#define TA_TARGET_O    8
+#define TA_TARGET_GATE 16             /* gate/up/down adapters are an extension: the reference wires */
+#define TA_TARGET_UP   32             /* q/k/v/o only (src/adapter/adapter_model.cu:82-87)           */
+#define TA_TARGET_DOWN 64
+#define TA_TARGETS_QKVO 15
+#define TA_TARGETS_ALL  127
+
+typedef struct ta_adapter_config {    /* AdapterConfig, include/tensor/adapter/adapter_config.hpp:25-70 */
+    int rank;
+    float alpha;                      /* effective scale = alpha / rank */
+    int targets;                      /* TA_TARGET_* bit mask */
+    float lr, grad_clip;
+    int warmup_steps;
+    float beta1, beta2, eps, weight_decay;
+    int centroid_modes;               /* bit 0: intended accumulator, bit 1: as-built accumulator */
+} ta_adapter_config;
+
+typedef struct ta_step_metrics {      /* StepMetrics, adapt_trainer.hpp:18-27 (wall-clock fields are the caller's) */
+    long step, tokens_consumed;
+    float loss;                       /* mean over per-token losses > 1e-9 (adapt_trainer.cu:237-246) */
+    float learning_rate;
+    float grad_norm;                  /* min(norm, grad_clip), as the reference reports (adapt_trainer.cu:250) */
+    float grad_norm_raw;
+} ta_step_metrics;
+
+typedef struct ta_trainer ta_trainer;
+
+/* AdaptTrainer::create (adapt_trainer.cu:280-286) + AdapterModel::create (adapter_model.cu:69-90):
+ * allocates the frozen-base arena, the flat LoRA arrays (FP32 master / m / v / grad + BF16 working)
+ * and an activation arena for micro-batches of `micro_batch` sequences of `seq_len` tokens.
+ * A is initialised with the reference's hash-Kaiming values and B with zeros; base weights are left
+ * uninitialised until ta_trainer_init_random() or uploads through ta_trainer_tensor(). */
+int ta_trainer_create(ta_ctx* ctx, const ta_model_config* model, const ta_adapter_config* adapter, int micro_batch,
+                      int seq_len, void* stream, ta_trainer** out);
+int ta_trainer_destroy(ta_trainer* tr);
+/* Random-init frozen base on the device: matrices and biases ~N(0, std), norm weights 1 (the
+ * reference loads these from safetensors, src/base/base_loader.cpp:112-166; synthetic here). */
+int ta_trainer_init_random(ta_trainer* tr, unsigned long long seed, float std);
+/* Device pointer and shape of a named tensor, for uploads / read-backs with cudaMemcpy:
+ *   "embed" "final_norm" "lm_head" "l<i>.{input_norm,post_norm,q_w,k_w,v_w,o_w,q_b,k_b,v_b,gate_w,up_w,down_w}"
+ *   "l<i>.lora.<q|k|v|o|gate|up|down>.<A|B|gA|gB|mA|mB|vA|vB|A_bf16|B_bf16>"
+ *   "lora.master" "lora.grad" "lora.m" "lora.v" "lora.working" (whole flat arrays)
+ *   "centroid.acc" "centroid.weight" "centroid_asbuilt.acc" "centroid_asbuilt.weight"
+ *   "l<i>.cache.<x_normed|Q|K|V|attn_out|r_in|r_mid>" "cache.dx_attn_in" (last micro-batch, layer 0)
+ * dtype: 0 = FP32, 1 = BF16. pitch is the row pitch in elements. */
+int ta_trainer_tensor(ta_trainer* tr, const char* name, void** dev_ptr, long* rows, long* cols, long* pitch, int* dtype);
+/* Re-derive the BF16 working copies from the FP32 masters (after masters were uploaded). */
+int ta_trainer_sync_working(ta_trainer* tr);
+/* AdapterModel::zero_grad (adapter_model.cu:222-229): one memset of the flat gradient array. */
+int ta_trainer_zero_grad(ta_trainer* tr);
+/* Steps 3-7 of do_step (adapt_trainer.cu:190-232) for `B` sequences of `T` tokens: zero_grad is NOT
+ * included (call ta_trainer_zero_grad once per optimiser step), so several calls accumulate.
+ * tokens / targets: B*T int32, HOST memory when host_inputs != 0 (copied H2D inside), else device.
+ * The batch is processed in micro-batches; the cross-entropy gradient is scaled by 1/global_tokens
+ * (pass B*T for a single GPU; the data-parallel caller passes the global count and then sum-reduces
+ * "lora.grad"). Centroid accumulation (per layer: hidden = post-input-norm activations, signal =
+ * d loss / d those activations, adapt_trainer.cu:210-232) runs on the device in the configured modes. */
+int ta_trainer_forward_backward(ta_trainer* tr, const int* tokens, const int* targets, int B, int T, long global_tokens,
+                                int host_inputs);
+/* compute_grad_norm + clip_gradients + AdamW::step_all (adapt_trainer.cu:248-253) then one D2H copy
+ * of {norm, loss sum, loss count}; fills *out. lr < 0 selects CosineSchedule::lr_at(step)
+ * (cosine_schedule.hpp:18-29) with total_steps given. Synchronises the stream. */
+int ta_trainer_optimizer_step(ta_trainer* tr, float lr, long total_steps, ta_step_metrics* out);
+/* AdaptTrainer::step (adapt_trainer.cu:130-277) on caller-provided ids: zero_grad + forward_backward +
+ * optimizer_step. */
+int ta_trainer_step(ta_trainer* tr, const int* tokens, const int* targets, int B, int T, float lr, long total_steps,
+                    int host_inputs, ta_step_metrics* out);
+/* CentroidAccumulator::write_snapshot (src/centroid/centroid_accumulator.cpp:72-91): normalised
+ * centroid acc/weight of the chosen mode (0 intended, 1 as-built) to `path` (may be NULL) in the
+ * reference's layout int32 D | D x f32 | f32 weight, and into centroid_out[D] / weight_out (host, may be
+ * NULL). Returns TA_OK without writing when the weight is zero, as the reference does. */
+int ta_trainer_write_snapshot(ta_trainer* tr, int mode, const char* path, float* centroid_out, float* weight_out);
+/* AdapterWriter::save_checkpoint / save_final (src/checkpoint/adapter_writer.cpp:130-159): writes
+ * adapter.safetensors (BF16 of the FP32 masters, flat shapes, reference tensor names), adapter.json
+ * and, unless final != 0, train_state.json into `dir`, byte-compatible with the reference's files. */
+int ta_trainer_save_checkpoint(ta_trainer* tr, const char* dir, const char* domain, long step, long tokens, int final_);
+/* "architecture" and "base_sha" written into adapter.json (BaseConfig::arch_name / base_sha). */
+int ta_trainer_set_meta(ta_trainer* tr, const char* arch_name, const char* base_sha);
+/* CentroidAccumulator::merge_and_write on the in-memory, chronological snapshot list
+ * (centroid_accumulator.cpp:93-168 as called from AdaptTrainer::save_adapter, adapt_trainer.cu:322-325). */
+int ta_trainer_merge_snapshots(ta_trainer* tr, int k, const char* out_path, int* passes);
+
+/* ── host-side logic mirrored from the reference ─────────────────────────────────────────── */
+/* CosineSchedule::lr_at (include/tensor/trainer/cosine_schedule.hpp:18-29). */
+float ta_cosine_lr(float base_lr, long warmup_steps, long total_steps, long step, float floor_frac);
+/* Assistant-only target masking (src/trainer/adapt_trainer.cu:145-182), in place on host arrays. */
+void ta_mask_targets(const int* input_ids, int* target_ids, int B, int T);
+/* k_kaiming_init_f32 (src/adapter/adapter_model.cu:28-39) on the host: out[rank*in_dim]. */
+void ta_kaiming_init_host(float* out, int in_dim, int rank, unsigned seed);
+/* CentroidMerge::run (src/centroid/centroid_merge.cpp:12-31): reads every *.centroid in `dir` (in
+ * directory-iteration order, as the reference does), clusters on the GPU with ta_kmeans_merge and
+ * writes int32 k | int32 D | k*D f32 to out_path. *n_vectors / *passes (may be NULL) report what ran. */
+int ta_centroid_merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, int k, int* n_vectors, int* passes);
+/* Host <-> device copies for callers without a CUDA runtime binding (synchronous). */
+int ta_memcpy_h2d(void* dst_dev, const void* src_host, size_t bytes);
+int ta_memcpy_d2h(void* dst_host, const void* src_dev, size_t bytes);
+
 #ifdef __cplusplus
 }
 #endif

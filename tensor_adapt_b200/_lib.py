@@ -69,6 +69,26 @@ _PROTOS = {
                                        c_float, P, c_int, P]),
     "ta_centroid_accumulate": (c_int, [P, c_int, P, P, c_int, c_int, P, P, P]),
     "ta_kmeans_merge": (c_int, [P, P, c_int, c_int, c_int, c_int, P, P, POINTER(c_int), POINTER(c_int), P]),
+    "ta_trainer_create": (c_int, [P, P, P, c_int, c_int, P, POINTER(c_void_p)]),
+    "ta_trainer_destroy": (c_int, [P]),
+    "ta_trainer_init_random": (c_int, [P, ctypes.c_ulonglong, c_float]),
+    "ta_trainer_tensor": (c_int, [P, c_char_p, POINTER(c_void_p), POINTER(c_long), POINTER(c_long), POINTER(c_long),
+                                  POINTER(c_int)]),
+    "ta_trainer_sync_working": (c_int, [P]),
+    "ta_trainer_zero_grad": (c_int, [P]),
+    "ta_trainer_forward_backward": (c_int, [P, P, P, c_int, c_int, c_long, c_int]),
+    "ta_trainer_optimizer_step": (c_int, [P, c_float, c_long, P]),
+    "ta_trainer_step": (c_int, [P, P, P, c_int, c_int, c_float, c_long, c_int, P]),
+    "ta_trainer_write_snapshot": (c_int, [P, c_int, c_char_p, P, P]),
+    "ta_trainer_save_checkpoint": (c_int, [P, c_char_p, c_char_p, c_long, c_long, c_int]),
+    "ta_trainer_set_meta": (c_int, [P, c_char_p, c_char_p]),
+    "ta_trainer_merge_snapshots": (c_int, [P, c_int, c_char_p, POINTER(c_int)]),
+    "ta_cosine_lr": (c_float, [c_float, c_long, c_long, c_long, c_float]),
+    "ta_mask_targets": (None, [P, P, c_int, c_int]),
+    "ta_kaiming_init_host": (None, [P, c_int, c_int, ctypes.c_uint]),
+    "ta_centroid_merge_dir": (c_int, [P, c_char_p, c_char_p, c_int, POINTER(c_int), POINTER(c_int)]),
+    "ta_memcpy_h2d": (c_int, [P, P, c_size_t]),
+    "ta_memcpy_d2h": (c_int, [P, P, c_size_t]),
     "ta_gemm_tokens_f32": (c_int, [P, c_int, c_int, c_int, c_float, P, c_long, P, c_long, P, c_long, c_int, c_int, P]),
 }
 

@@ -1,0 +1,139 @@
+"""Full training step of the CUDA trainer (C ABI) against (a) the NumPy oracle and (b), when the
+compiled reference is present (oracle/_ref/ref_harness), the unmodified reference run on the same GPU
+with the same seeded weights.
+
+Tolerances are the north star's: loss within 1e-2 relative, LoRA gradients cosine >= 0.999 and
+max|err| <= 2e-2 * max|ref| (per tensor, on tensors whose gradient is not numerically negligible),
+centroid vectors within 1e-3 relative L2, masters after AdamW: an Adam step moves every weight by
+about lr regardless of gradient size, so they are compared as |delta| <= 2.2 * lr."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+import refcase as rc
+import ta_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+HAVE_REF = os.path.exists(rc.HARNESS)
+
+
+def run_cuda(ctx, cfg, base, adapter, toks, tgts, B, T, rank, alpha, targets, lr, wd=0.01, micro=None, modes=3,
+             grad_clip=1.0):
+    from tensor_adapt_b200.trainer import AdaptTrainer, AdapterConfig, TARGET_BITS
+    bits = sum(TARGET_BITS[t] for t in targets)
+    ac = AdapterConfig.defaults(rank=rank, alpha=alpha, targets=bits, lr=lr, weight_decay=wd, centroid_modes=modes,
+                                grad_clip=grad_clip)
+    tr = AdaptTrainer(ctx, rc.model_config(cfg), ac, micro or B, T)
+    rc.load_into_trainer(tr, cfg, base, adapter)
+    out = []
+    for s in range(len(toks)):
+        tr.zero_grad()
+        tr.forward_backward(toks[s], tgts[s], B)
+        grads = {(l, t): (tr.download(f"l{l}.lora.{t}.gA"), tr.download(f"l{l}.lora.{t}.gB"))
+                 for l in range(cfg.layers) for t in targets}
+        loss_tok = tr.download("cache.loss").ravel()[: (micro or B) * T]
+        m = tr.optimizer_step(lr)
+        masters = {(l, t): (tr.download(f"l{l}.lora.{t}.A"), tr.download(f"l{l}.lora.{t}.B"))
+                   for l in range(cfg.layers) for t in targets}
+        cen = {mode: tr.write_snapshot(s + 1, mode) for mode in (0, 1)}
+        out.append(dict(m=m, grads=grads, masters=masters, cen=cen, loss_tok=loss_tok))
+    ctx.check_device()
+    return tr, out
+
+
+def check_grads(got, ref, label):
+    gmax = max(np.abs(r).max() for pair in ref.values() for r in pair)
+    for key in ref:
+        for i, nm in enumerate(("gA", "gB")):
+            g, r = got[key][i], ref[key][i]
+            if np.abs(r).max() < 1e-3 * gmax:
+                continue   # numerically negligible tensor: cosine is ill-conditioned
+            assert rc.cosine(g, r) >= 0.999, (label, key, nm, rc.cosine(g, r))
+            assert rc.relmax(g, r) <= 2e-2, (label, key, nm, rc.relmax(g, r))
+
+
+@pytest.mark.parametrize("targets,rank,hd", [(("q", "k", "v", "o"), 16, 64), (o.ALL_TARGETS, 16, 128),
+                                              (("q", "k", "v", "o"), 4, 64)])
+def test_step_vs_oracle(ctx, targets, rank, hd):
+    cfg = rc.tiny_cfg(hd=hd, hq=4, hkv=2, hidden=128)
+    B, T, alpha, lr = 2, 128, 2.0 * rank, 2e-4
+    base, adapter, toks, tgts = rc.make_case(cfg, B, T, rank, targets, seed=1, steps=2)
+    tr, got = run_cuda(ctx, cfg, base, adapter, toks, tgts, B, T, rank, alpha, targets, lr)
+    ci, ca = o.CentroidAccumulator(cfg.hidden), o.CentroidAccumulator(cfg.hidden)
+    for s in range(2):
+        ref = o.train_step(cfg, base, adapter, toks[s], tgts[s], B, T, alpha=alpha, rank=rank, lr=lr, step=s + 1, wd=0.01,
+                           centroid_intended=ci, centroid_asbuilt=ca)
+        g = got[s]
+        assert abs(g["m"].loss - ref["mean_loss"]) <= 1e-2 * ref["mean_loss"]
+        assert abs(g["m"].grad_norm_raw - ref["grad_norm"]) <= 2e-2 * ref["grad_norm"]
+        refg = {(l, t): ref["grads"][l * len(targets) + i] for l in range(cfg.layers) for i, t in enumerate(targets)}
+        check_grads(g["grads"], refg, f"step{s}")
+        for (l, t), (A, Bm) in g["masters"].items():
+            lp = adapter[l][t]
+            assert np.abs(A - lp.A_f32).max() <= 2.2 * lr and np.abs(Bm - lp.B_f32).max() <= 2.2 * lr
+        for mode, acc in ((0, ci), (1, ca)):
+            cen, w = g["cen"][mode]
+            refc = acc.acc / acc.weight[0]
+            assert np.linalg.norm(cen - refc) <= 1e-3 * np.linalg.norm(refc) + 1e-6, (mode, s)
+            assert abs(w - acc.weight[0]) <= 1e-2 * acc.weight[0]
+    tr.close()
+
+
+def test_micro_batching_matches_single_pass(ctx):
+    """Gradient accumulation over micro-batches (1/global-token CE scale) equals the one-pass result."""
+    cfg = rc.tiny_cfg()
+    B, T, rank = 4, 128, 16
+    base, adapter, toks, tgts = rc.make_case(cfg, B, T, rank, seed=2)
+    t1, a = run_cuda(ctx, cfg, base, adapter, toks, tgts, B, T, rank, 32.0, ("q", "k", "v", "o"), 2e-4)
+    t2, b = run_cuda(ctx, cfg, base, adapter, toks, tgts, B, T, rank, 32.0, ("q", "k", "v", "o"), 2e-4, micro=1)
+    check_grads(b[0]["grads"], a[0]["grads"], "micro")
+    assert abs(a[0]["m"].loss - b[0]["m"].loss) <= 1e-4 * a[0]["m"].loss
+    t1.close(); t2.close()
+
+
+def test_step_is_deterministic(ctx):
+    cfg = rc.tiny_cfg()
+    base, adapter, toks, tgts = rc.make_case(cfg, 2, 128, 16, seed=3)
+    t1, a = run_cuda(ctx, cfg, base, adapter, toks, tgts, 2, 128, 16, 32.0, ("q", "k", "v", "o"), 2e-4)
+    t2, b = run_cuda(ctx, cfg, base, adapter, toks, tgts, 2, 128, 16, 32.0, ("q", "k", "v", "o"), 2e-4)
+    for key in a[0]["grads"]:
+        assert np.array_equal(a[0]["grads"][key][0], b[0]["grads"][key][0])
+        assert np.array_equal(a[0]["grads"][key][1], b[0]["grads"][key][1])
+    t1.close(); t2.close()
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="compiled reference (oracle/_ref/ref_harness) not present")
+@pytest.mark.parametrize("hd,T", [(64, 128), (128, 256)])
+def test_step_vs_reference_binary(ctx, hd, T):
+    cfg = rc.tiny_cfg(hd=hd)
+    B, rank, alpha, lr = 2, 16, 32.0, 2e-4
+    targets = ("q", "k", "v", "o")
+    base, adapter, toks, tgts = rc.make_case(cfg, B, T, rank, targets, seed=4, steps=2)
+    with tempfile.TemporaryDirectory() as d:
+        rc.write_case_dir(d + "/case", cfg, base, adapter, toks, tgts, B, T, rank, alpha, lr=lr, wd=0.01, grad_clip=1.0)
+        rc.run_harness("step", d + "/case", d + "/out")
+        _, got = run_cuda(ctx, cfg, base, adapter, toks, tgts, B, T, rank, alpha, targets, lr)
+        ref_loss = rc.f32(d + "/out/loss.bin")
+        assert abs(got[0]["m"].loss - o.mean_loss(ref_loss)) <= 1e-2 * o.mean_loss(ref_loss)
+        refg = {}
+        for l in range(cfg.layers):
+            for t in targets:
+                i, od = o.target_dims(cfg, t)
+                refg[(l, t)] = (rc.f32(f"{d}/out/l{l}_lora_{t}_gA.bin", (rank, i)), rc.f32(f"{d}/out/l{l}_lora_{t}_gB.bin", (od, rank)))
+        check_grads(got[0]["grads"], refg, "reference")
+        assert abs(got[0]["m"].grad_norm_raw - rc.f32(d + "/out/grad_norm.bin")[0]) <= 2e-2 * got[0]["m"].grad_norm_raw
+        for s in range(2):
+            for l in range(cfg.layers):
+                for t in targets:
+                    i, od = o.target_dims(cfg, t)
+                    A = rc.f32(f"{d}/out/after_step_{s}/l{l}_lora_{t}_A.bin", (rank, i))
+                    Bm = rc.f32(f"{d}/out/after_step_{s}/l{l}_lora_{t}_B.bin", (od, rank))
+                    gA, gB = got[s]["masters"][(l, t)]
+                    assert np.abs(gA - A).max() <= 2.2 * lr and np.abs(gB - Bm).max() <= 2.2 * lr
+            for mode, sub in ((0, "centroids_intended"), (1, "centroids_asbuilt")):
+                refc, refw = o.read_snapshot_file(f"{d}/out/{sub}/step-{s + 1}.centroid")
+                cen, w = got[s]["cen"][mode]
+                assert np.linalg.norm(cen - refc) <= 1e-3 * np.linalg.norm(refc) + 1e-6, (mode, s)
