@@ -127,12 +127,6 @@ static Tensor load_f32(const std::string& path, core::Shape shape, const Device&
     if (b.size() != v.nbytes()) { std::cerr << "size mismatch " << path << "\n"; std::exit(2); }
     return Tensor::from_host(v, dev);
 }
-static Tensor load_i32(const std::string& path, core::Shape shape, const Device& dev) {
-    auto b = slurp(path);
-    core::TensorView v{b.data(), DType::I32, shape};
-    if (b.size() != v.nbytes()) { std::cerr << "size mismatch " << path << "\n"; std::exit(2); }
-    return Tensor::from_host(v, dev);
-}
 
 // ───────────────────────── model construction ─────────────────────────
 
@@ -309,6 +303,7 @@ struct StepOut { float norm; double ms; };
 static int mode_step(const std::string& dir, const std::string& out, bool bench) {
     auto c = read_cfg(dir);
     Device dev = Device::open("cuda:0");
+    std::cerr << "[harness] dev.sm_major()=" << dev.sm_major() << " (>= 8 selects the batched cuBLAS SDPA path)\n";
     base::FrozenBase b = make_base(c, dir, dev);
     adapter::AdapterConfig a = make_acfg(c);
     adapter::AdapterModel m = adapter::AdapterModel::create(b, a, dev);
@@ -368,9 +363,8 @@ static int mode_step(const std::string& dir, const std::string& out, bool bench)
             }
         }
         dev.sync();
-        float norm = grad_norm_and_clip(m, a.grad_clip, dev);
         if (!bench && s == 0) {
-            // dumps taken before the optimiser touches anything
+            // dumps taken before clipping scales the gradients and before the optimiser touches anything
             dump_tensor(out + "/loss.bin", loss);
             if (geti(c, "dump_logits", 0)) dump_tensor(out + "/logits.bin", fwd.logits);
             if (geti(c, "dump_acts", 0)) {
@@ -383,6 +377,7 @@ static int mode_step(const std::string& dir, const std::string& out, bool bench)
                 dump_tensor(out + "/l0_dQ.bin", lg[0].dQ);
                 dump_tensor(out + "/l0_dK.bin", lg[0].dK);
                 dump_tensor(out + "/l0_dV.bin", lg[0].dV);
+                dump_tensor(out + "/l0_do_proj.bin", lg[0].do_proj);
             }
             for (std::size_t l = 0; l < m.layers.size(); l++)
                 for (int i = 0; i < 4; i++) {
@@ -390,8 +385,9 @@ static int mode_step(const std::string& dir, const std::string& out, bool bench)
                     std::string p = out + "/l" + std::to_string(l) + "_lora_" + PN[i];
                     dump_tensor(p + "_gA.bin", lp->gA); dump_tensor(p + "_gB.bin", lp->gB);
                 }
-            dump(out + "/grad_norm.bin", &norm, 4);
         }
+        float norm = grad_norm_and_clip(m, a.grad_clip, dev);
+        if (!bench && s == 0) dump(out + "/grad_norm.bin", &norm, 4);
         opt.step_all(m, a.lr, s + 1, dev);
         cudaEventRecord(e1, dev.stream());
         dev.sync();

@@ -15,6 +15,7 @@
 // work with one thread per tile row (TMEM lane).  Every wait is bounded.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 
 #include "ctx.h"
 #include "ptx.cuh"
@@ -673,6 +674,7 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
         delta = static_cast<float*>(ws);
     }
     const long warps = long(B) * T * Hq;
+    if (!(delta_scratch && getenv("TA_DEBUG_KEEP_DELTA")))
     attn_delta_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(out), delta, B, T, Hq, head_dim);
     TA_LAUNCH_CHECK(ctx, "attn_delta_kernel");

@@ -449,6 +449,10 @@ int ta_trainer_tensor(ta_trainer* t, const char* name, void** dev_ptr, long* row
     else if (n == "centroid_asbuilt.weight") set(t->cen_w_ab, 1, 1, 0);
     else if (n == "cache.dx_attn_in") set(t->d_xn, BT, H, 1);
     else if (n == "cache.loss") set(t->loss, 1, BT, 0);
+    else if (n == "cache.dQ") set(t->dQ, BT, qd, 1);
+    else if (n == "cache.dK") set(t->dK, BT, kv, 1);
+    else if (n == "cache.dV") set(t->dV, BT, kv, 1);
+    else if (n == "cache.d_attn_out") set(t->d_attn, BT, qd, 1);
     else if (std::sscanf(name, "l%d.%63s", &l, rest) == 2 && l >= 0 && l < c.layers) {
         std::string f(rest);
         LayerW& w = t->L[l];

@@ -56,7 +56,7 @@ def run_harness(mode, case_dir, out_dir):
     r = subprocess.run([HARNESS, mode, case_dir, out_dir], capture_output=True, text=True, timeout=1800)
     if r.returncode != 0:
         raise RuntimeError(f"ref_harness {mode} failed: {r.stderr[-2000:]}")
-    return r.stdout
+    return r.stdout + r.stderr
 
 
 def f32(path, shape=None):
