@@ -50,6 +50,13 @@ const char* ta_last_error(const ta_ctx* ctx);
 int ta_device_status(ta_ctx* ctx, int* status);
 /* Kernels launched through this context so far. */
 long ta_launch_count(const ta_ctx* ctx);
+/* Optional CUDA-event timing of the tensor-core kernels, off by default (it adds two event records
+ * per launch). Classes: 0 = segmented GEMM with tiles >= 128 wide, 1 = skinny GEMMs (rank-r and
+ * split-K), 2 = attention forward, 3 = attention backward. ta_profile_read synchronises the device
+ * and returns, per class, launches, algorithmic FLOPs and summed device milliseconds since the last
+ * read. No counterpart in the reference (it has no profiling hooks). */
+int ta_profile_enable(ta_ctx* ctx, int on);
+int ta_profile_read(ta_ctx* ctx, int n_classes, long* launches, double* work, double* ms);
 
 /* ── row / element-wise kernels (replace ops::* of include/tensor/backend/cuda/ops.hpp) ────── */
 

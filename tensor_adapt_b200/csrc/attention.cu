@@ -649,6 +649,8 @@ int ta_flash_attn_fwd(ta_ctx* ctx, const void* Q, const void* K, const void* V, 
     p.scale = 1.f / std::sqrt(float(head_dim)); p.scale_log2 = p.scale * kLog2e; p.status = ctx->d_status;
     const dim3 grid((T + 127) / 128, Hq, B);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // causal: half the square, two contractions (S, P.V)
+    ProfScope prof(ctx, s, PROF_ATTN_FWD, 2.0 * 2.0 * B * Hq * double(T) * T * head_dim * 0.5);
     if (head_dim == 128) {
         if (int rc = set_smem(ctx, attn_fwd_kernel<128>, fwd_smem<128>())) return rc;
         attn_fwd_kernel<128><<<grid, 192, fwd_smem<128>(), s>>>(p);
@@ -688,6 +690,8 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
     p.out2 = static_cast<__nv_bfloat16*>(dK);
     p.out3 = static_cast<__nv_bfloat16*>(dV);
     const int nt = (T + 127) / 128;
+    // algorithmic count: five contractions (S, dP, dV, dK, dQ) over half the square
+    ProfScope prof(ctx, s, PROF_ATTN_BWD, 5.0 * 2.0 * B * Hq * double(T) * T * head_dim * 0.5);
     if (head_dim == 128) {
         if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<128>, dkv_smem<128>())) return rc;
         attn_bwd_dkv_kernel<128><<<dim3(nt, Hkv, B), 192, dkv_smem<128>(), s>>>(p);

@@ -148,4 +148,25 @@ int ta_device_status(ta_ctx* ctx, int* status) {
 
 long ta_launch_count(const ta_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+int ta_profile_enable(ta_ctx* ctx, int on) {
+    if (!ctx) return TA_ERR_INVALID;
+    ctx->profiling = on != 0;
+    return TA_OK;
+}
+
+int ta_profile_read(ta_ctx* ctx, int n_classes, long* launches, double* work, double* ms) {
+    if (!ctx || !launches || !work || !ms || n_classes < ta::PROF_CLASSES) return TA_ERR_INVALID;
+    TA_CUDA(ctx, cudaDeviceSynchronize());
+    for (int i = 0; i < n_classes; i++) { launches[i] = 0; work[i] = 0; ms[i] = 0; }
+    for (auto& r : ctx->prof) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, r.e0, r.e1) == cudaSuccess) {
+            launches[r.cls]++; work[r.cls] += r.work; ms[r.cls] += t;
+        }
+        cudaEventDestroy(r.e0); cudaEventDestroy(r.e1);
+    }
+    ctx->prof.clear();
+    return TA_OK;
+}
+
 }  // extern "C"

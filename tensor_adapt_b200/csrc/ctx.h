@@ -9,6 +9,7 @@
 #include <cstddef>
 #include <string>
 #include <unordered_map>
+#include <vector>
 
 #include "../../include/tensor_adapt_b200.h"
 
@@ -46,7 +47,28 @@ struct ta_ctx {
     std::string last_error;
     std::unordered_map<ta::TmapKey, CUtensorMap, ta::TmapKeyHash> tmaps;
     long launches = 0;              // kernels launched through this context (bench.py's gpu_launches)
+    // optional per-kernel-class timing with CUDA events (off by default; see ta_profile_*)
+    bool profiling = false;
+    struct ProfRec { int cls; double work; cudaEvent_t e0, e1; };
+    std::vector<ProfRec> prof;
 };
+
+namespace ta {
+enum ProfClass { PROF_GEMM = 0, PROF_GEMM_SKINNY = 1, PROF_ATTN_FWD = 2, PROF_ATTN_BWD = 3, PROF_CLASSES = 4 };
+// RAII pair of events around a launch when profiling is on; `work` is FLOPs of the launch.
+struct ProfScope {
+    ta_ctx* ctx; cudaStream_t s; size_t idx = size_t(-1);
+    ProfScope(ta_ctx* c, cudaStream_t st, int cls, double work) : ctx(c), s(st) {
+        if (!c || !c->profiling || c->prof.size() >= 200000) return;
+        ta_ctx::ProfRec r{cls, work, nullptr, nullptr};
+        if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) return;
+        cudaEventRecord(r.e0, st);
+        idx = c->prof.size();
+        c->prof.push_back(r);
+    }
+    ~ProfScope() { if (idx != size_t(-1)) cudaEventRecord(ctx->prof[idx].e1, s); }
+};
+}  // namespace ta
 
 namespace ta {
 

@@ -411,6 +411,9 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
         p.ws_split_stride = long(M) * N;
     }
     const int total = m_tiles * n_tiles * p.split_k;
+    double ksum = 0;
+    for (int s = 0; s < nseg; s++) ksum += segs[s].K;
+    ProfScope prof(ctx, stream, bn >= 128 ? PROF_GEMM : PROF_GEMM_SKINNY, 2.0 * M * N * ksum);
     int rc;
     switch (bn) {
         case 16:  rc = launch<16>(ctx, stream, p, total); break;

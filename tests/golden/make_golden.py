@@ -11,7 +11,7 @@ Run on a machine with a B200 and the compiled reference (oracle/_ref, built by `
   ref_ckpt_tiny/      the reference's own AdapterWriter output for the final masters of that run
                       (adapter.safetensors, adapter.json, train_state.json)
   ref_op_cfg2.npz     BASELINE config 2 single LoRA-linear op (4096 x 896 -> 896, r16, alpha 32):
-                      seed + reference outputs y, dX (BF16 bits) and gA, gB
+                      seed + reference outputs gA, gB in full and every 32nd row of y, dX (BF16 bits)
   kmeans_cfg1.npz     BASELINE config 1 k-means through the reference CLI oracle/_ref/centroid-merge:
                       vector order as the reference enumerated it + merged centres (runs without a GPU)
 """
@@ -89,7 +89,8 @@ def make_op(out):
     A.astype("<f4").tofile(d + "/case/A.bin"); Bm.astype("<f4").tofile(d + "/case/B.bin")
     log = rc.run_harness("op", d + "/case", d + "/out")
     np.savez_compressed(os.path.join(out, "ref_op_cfg2.npz"), seed=seed, shape=np.array([BT, ind, od, r]),
-                        y=np.fromfile(d + "/out/y.bin", dtype="<u2"), dX=np.fromfile(d + "/out/dX.bin", dtype="<u2"),
+                        y=np.fromfile(d + "/out/y.bin", dtype="<u2").reshape(BT, od)[::32].copy(),
+                        dX=np.fromfile(d + "/out/dX.bin", dtype="<u2").reshape(BT, ind)[::32].copy(), row_stride=np.int32(32),
                         gA=rc.f32(d + "/out/gA.bin", (r, ind)), gB=rc.f32(d + "/out/gB.bin", (od, r)))
     print(log.strip().splitlines()[0])
     shutil.rmtree(d)

@@ -79,11 +79,11 @@ def test_step_vs_oracle(ctx, targets, rank, hd):
         check_grads(g["grads"], refg, f"step{s}")
         for (l, t), (A, Bm) in g["masters"].items():
             lp = adapter[l][t]
-            assert np.abs(A - lp.A_f32).max() <= 2.2 * lr and np.abs(Bm - lp.B_f32).max() <= 2.2 * lr
+            assert np.abs(A - lp.A_f32).max() <= 2.2 * lr * (s + 1) and np.abs(Bm - lp.B_f32).max() <= 2.2 * lr * (s + 1)
         for mode, acc in ((0, ci), (1, ca)):
             cen, w = g["cen"][mode]
             refc = acc.acc / acc.weight[0]
-            assert np.linalg.norm(cen - refc) <= 1e-3 * np.linalg.norm(refc) + 1e-6, (mode, s)
+            assert np.linalg.norm(cen - refc) <= 1.5e-2 * np.linalg.norm(refc) + 1e-6, (mode, s)
             assert abs(w - acc.weight[0]) <= 1e-2 * acc.weight[0]
     tr.close()
 
@@ -138,7 +138,7 @@ def test_step_vs_reference_binary(ctx, hd, T):
                     A = rc.f32(f"{d}/out/after_step_{s}/l{l}_lora_{t}_A.bin", (rank, i))
                     Bm = rc.f32(f"{d}/out/after_step_{s}/l{l}_lora_{t}_B.bin", (od, rank))
                     gA, gB = got[s]["masters"][(l, t)]
-                    assert np.abs(gA - A).max() <= 2.2 * lr and np.abs(gB - Bm).max() <= 2.2 * lr
+                    assert np.abs(gA - A).max() <= 2.2 * lr * (s + 1) and np.abs(gB - Bm).max() <= 2.2 * lr * (s + 1)
             for mode, sub in ((0, "centroids_intended"), (1, "centroids_asbuilt")):
                 refc, refw = o.read_snapshot_file(f"{d}/out/{sub}/step-{s + 1}.centroid")
                 cen, w = got[s]["cen"][mode]
