@@ -109,6 +109,22 @@ int ta_gemm_bf16(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, l
  * transpose_out != 0 stores C^T (C is then [N][ldc]). */
 int ta_gemm_tokens_f32(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, long lda, const void* B, long ldb,
                        float* C, long ldc, int accumulate, int transpose_out, void* stream);
+/* The same product for callers that cannot allocate device memory (a CUDA-graph capture in progress,
+ * a host application that owns all of device memory through its own pool, a plugin sandbox that forbids
+ * cudaMalloc and the device-wide synchronisation it implies).  It has no counterpart in the reference,
+ * whose every op allocates its temporaries (src/adapter/adapter_model.cu:142-191).  Same arguments and
+ * results as ta_gemm_tokens_f32, but the split-K partials live in a fixed array inside the library image
+ * (TA_STATIC_SCRATCH_BYTES, held by every GPU that loads the library until exit) and the call performs no
+ * cudaMalloc/cudaFree and inserts nothing into the tensor-map cache.
+ *   - sizes whose partials (splits * M * N * 4 bytes) exceed TA_STATIC_SCRATCH_BYTES are rejected with
+ *     TA_ERR_NOMEM and a message naming the sizes; use ta_gemm_tokens_f32 for those;
+ *   - the context's device must be the current device; the FIRST call on a device resolves the array's
+ *     device address (cudaGetSymbolAddress) - make that first call before any stream capture begins;
+ *   - all calls share the one array: calls that may overlap on the GPU (different streams, or graphs
+ *     replayed concurrently) race on it and must be serialised by the caller. */
+#define TA_STATIC_SCRATCH_BYTES (8u << 20)
+int ta_gemm_tokens_f32_static(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, long lda, const void* B,
+                              long ldb, float* C, long ldc, int accumulate, int transpose_out, void* stream);
 
 /* ── LoRA-augmented projection ─────────────────────────────────────────────────────────────
  * proj_fwd + ops::add_bias + AdapterModel::apply_lora_fwd (src/base/arch/qwen2.cu:21-30,95-108;

@@ -91,6 +91,8 @@ _PROTOS = {
     "ta_centroid_merge_dir": (c_int, [P, c_char_p, c_char_p, c_int, POINTER(c_int), POINTER(c_int)]),
     "ta_memcpy_h2d": (c_int, [P, P, c_size_t]),
     "ta_memcpy_d2h": (c_int, [P, P, c_size_t]),
+    "ta_gemm_tokens_f32_static": (c_int, [P, c_int, c_int, c_int, c_float, P, c_long, P, c_long, P, c_long, c_int, c_int,
+                                          P]),
     "ta_gemm_tokens_f32": (c_int, [P, c_int, c_int, c_int, c_float, P, c_long, P, c_long, P, c_long, c_int, c_int, P]),
 }
 

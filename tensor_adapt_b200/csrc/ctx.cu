@@ -32,14 +32,8 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-int get_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0,
-                  uint32_t box1, CUtensorMap* out) {
-    TmapKey key{ptr, dim0, dim1, pitch_bytes, box0, box1};
-    auto it = ctx->tmaps.find(key);
-    if (it != ctx->tmaps.end()) {
-        *out = it->second;
-        return TA_OK;
-    }
+int encode_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0,
+                     uint32_t box1, CUtensorMap* out) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(ctx, TA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (pitch_bytes & 15))
@@ -48,8 +42,7 @@ int get_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, ui
     cuuint64_t gstride[1] = {pitch_bytes};
     cuuint32_t box[2] = {box0, box1};
     cuuint32_t estr[2] = {1, 1};
-    CUtensorMap m;
-    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -59,6 +52,19 @@ int get_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, ui
                       box1);
         return fail(ctx, TA_ERR_CUDA, buf);
     }
+    return TA_OK;
+}
+
+int get_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0,
+                  uint32_t box1, CUtensorMap* out) {
+    TmapKey key{ptr, dim0, dim1, pitch_bytes, box0, box1};
+    auto it = ctx->tmaps.find(key);
+    if (it != ctx->tmaps.end()) {
+        *out = it->second;
+        return TA_OK;
+    }
+    CUtensorMap m;
+    if (int rc = encode_tmap_bf16(ctx, ptr, dim0, dim1, pitch_bytes, box0, box1, &m)) return rc;
     if (ctx->tmaps.size() > 8192) ctx->tmaps.clear();
     ctx->tmaps.emplace(key, m);
     *out = m;

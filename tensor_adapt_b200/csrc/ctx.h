@@ -80,6 +80,10 @@ int check_cuda(ta_ctx* ctx, cudaError_t e, const char* what);
 int get_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0,
                   uint32_t box1, CUtensorMap* out);
 
+// Same map, encoded straight into *out without touching the cache (no host allocation).
+int encode_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0,
+                     uint32_t box1, CUtensorMap* out);
+
 // Scratch of at least `bytes`, grown on demand when the context owns its workspace.
 int get_workspace(ta_ctx* ctx, size_t bytes, void** out);
 

@@ -378,6 +378,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
         if ((g.a_mn && (M % 8)) || (!g.a_mn && false))
             return fail(ctx, TA_ERR_INVALID, "seg_gemm: MN-major A needs M % 8 == 0");
         int rc;
+        auto get_tmap_bf16 = out.no_host_state ? encode_tmap_bf16 : ta::get_tmap_bf16;
         if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, 128, &p.tmA[s]);
         else         rc = get_tmap_bf16(ctx, g.A, uint64_t(M), uint64_t(g.K), uint64_t(g.lda) * 2, 64, 64, &p.tmA[s]);
         if (rc) return rc;
@@ -413,7 +414,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     const int total = m_tiles * n_tiles * p.split_k;
     double ksum = 0;
     for (int s = 0; s < nseg; s++) ksum += segs[s].K;
-    ProfScope prof(ctx, stream, bn >= 128 ? PROF_GEMM : PROF_GEMM_SKINNY, 2.0 * M * N * ksum);
+    ProfScope prof(out.no_host_state ? nullptr : ctx, stream, bn >= 128 ? PROF_GEMM : PROF_GEMM_SKINNY, 2.0 * M * N * ksum);
     int rc;
     switch (bn) {
         case 16:  rc = launch<16>(ctx, stream, p, total); break;

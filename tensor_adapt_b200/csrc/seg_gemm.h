@@ -41,6 +41,7 @@ struct GemmOut {
     bool transpose_out = false;         // split-K reduce only: write C[n][m] (C is [N][ldc])
     float* split_ws = nullptr;          // split-K partials go here instead of the context workspace
     size_t split_ws_bytes = 0;
+    bool no_host_state = false;         // encode tensor maps on the stack: no cache insert, no profiling events
 };
 
 // Split count the token-contracted gradient GEMM (M x N output, K tokens) should use, and the bytes
