@@ -27,7 +27,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 struct AttnParams {
-    CUtensorMap tmQ, tmK, tmV, tmdO;
+    CUtensorMap tmQ, tmK, tmV, tmdO;          // boxes of 128 rows
+    CUtensorMap tmQ64, tmK64, tmV64, tmdO64;  // boxes of 64 rows (backward sub-tiles)
     __nv_bfloat16* out;        // fwd: O ; dq: dQ
     __nv_bfloat16* out2;       // dkv: dK
     __nv_bfloat16* out3;       // dkv: dV
@@ -38,8 +39,8 @@ struct AttnParams {
     int* status;
 };
 
-// byte offset of element (row, col) of a [128][128]-element BF16 operand stored as two K-major
-// 64-column chunks of [128 rows][128 B] with the 128-byte swizzle (16-byte units XOR row%8)
+// byte offset of element (row, col) of a BF16 operand stored as K-major 64-column chunks of
+// [128 rows][128 B] with the 128-byte swizzle (16-byte units XOR row%8)
 __device__ __forceinline__ uint32_t kmajor_off(int row, int col) {
     const int chunk = col >> 6, c = col & 63;
     return uint32_t(chunk) * 16384u + uint32_t(row) * 128u + uint32_t(((c >> 3) ^ (row & 7)) << 4) + uint32_t(c & 7) * 2u;
@@ -48,42 +49,51 @@ __device__ __forceinline__ uint32_t kmajor_off(int row, int col) {
 template <int HD>
 struct Tile {
     static constexpr int NC = HD / 64;
-    static constexpr uint32_t BYTES = NC * 16384u;
+    static constexpr uint32_t BYTES = NC * 16384u;     // [128 rows][HD]
+    static constexpr uint32_t BYTES64 = NC * 8192u;    // [64 rows][HD]
 };
 
-// D[128, N] (+)= A[128, HD] . B[N=128, HD]^T, both K-major tiles of NC 64-column chunks
-template <int HD>
-__device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, bool accumulate) {
-    constexpr uint32_t idesc = umma_idesc_bf16(128, 128, false, false);
+// D[128, N] (+)= A[128, HD] . B[N, HD]^T, both K-major, NC chunks of a_chunk / b_chunk bytes
+template <int HD, int N>
+__device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_smem, uint32_t a_chunk, uint32_t b_smem,
+                                       uint32_t b_chunk, bool accumulate) {
+    constexpr uint32_t idesc = umma_idesc_bf16(128, N, false, false);
 #pragma unroll
     for (int c = 0; c < Tile<HD>::NC; c++)
 #pragma unroll
         for (int ki = 0; ki < 4; ki++)
-            umma_bf16(d_tmem, smem_desc_sw128(a_smem + c * 16384 + ki * 32, 16, 1024),
-                      smem_desc_sw128(b_smem + c * 16384 + ki * 32, 16, 1024), idesc, (accumulate || c || ki) ? 1u : 0u);
+            umma_bf16(d_tmem, smem_desc_sw128(a_smem + c * a_chunk + ki * 32, 16, 1024),
+                      smem_desc_sw128(b_smem + c * b_chunk + ki * 32, 16, 1024), idesc, (accumulate || c || ki) ? 1u : 0u);
 }
 
-// D[128, HD] (+)= A[128, 128] . B[128 (k), HD (n)]: A K-major (two 64-column chunks), B is a
-// [128 rows][HD] tile read MN-major (n chunks 16384 B apart, 8-row groups 1024 B apart)
-template <int HD>
-__device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, bool accumulate) {
+// D[128, HD] (+)= A[128, KT] . B[KT (k), HD (n)]: A K-major (64-column chunks 16384 B apart), B a
+// [KT rows][HD] tile read MN-major (n chunks b_chunk bytes apart, 8-row groups 1024 B apart)
+template <int HD, int KT>
+__device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, uint32_t b_chunk,
+                                        bool accumulate) {
     constexpr uint32_t idesc = umma_idesc_bf16(128, HD, false, true);
 #pragma unroll
-    for (int ks = 0; ks < 8; ks++)
+    for (int ks = 0; ks < KT / 16; ks++)
         umma_bf16(d_tmem, smem_desc_sw128(a_smem + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                  smem_desc_sw128(b_smem + ks * 2048, 16384, 1024), idesc, (accumulate || ks) ? 1u : 0u);
+                  smem_desc_sw128(b_smem + ks * 2048, b_chunk, 1024), idesc, (accumulate || ks) ? 1u : 0u);
 }
 
 template <int HD>
-__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col0, int row0) {
+__device__ __forceinline__ void load_tile(uint8_t* dst, uint32_t chunk_bytes, const CUtensorMap* tm, uint64_t* bar,
+                                          int col0, int row0) {
 #pragma unroll
-    for (int c = 0; c < Tile<HD>::NC; c++) tma_load_2d(dst + c * 16384, tm, bar, col0 + 64 * c, row0);
+    for (int c = 0; c < Tile<HD>::NC; c++) tma_load_2d(dst + c * chunk_bytes, tm, bar, col0 + 64 * c, row0);
 }
 
 #define ATT_WAIT(bar, parity, code) \
     if (!mbar_wait((bar), (parity), abort_flag, p.status, (code))) goto done
 
+// A running maximum is only raised when the new one exceeds it by more than this (log2 units): the
+// probabilities then stay below 2^8 and the accumulator in TMEM rarely needs rescaling.
+constexpr float kRescaleThreshold = 8.f;
+
 // ─────────────────────────────── forward ───────────────────────────────
+// TMEM: S buffers at columns [0,128) and [128,256), O accumulator at [256, 256+HD).
 
 template <int HD>
 __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
@@ -93,13 +103,16 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
-             *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 14, *o_empty = bars + 15;
+             *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 14;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = gridDim.x - 1 - blockIdx.x;   // heavy (late) query tiles first
-    const int h = blockIdx.y, b = blockIdx.z;
+    // 1-D grid ordered heavy-first over the WHOLE launch: late query tiles (most key tiles) of every
+    // (head, batch) come before any lighter tile
+    const int nt = (p.T + 127) / 128, hb = p.Hq * p.B;
+    const int qt = nt - 1 - int(blockIdx.x) / hb;
+    const int h = (int(blockIdx.x) % hb) % p.Hq, b = (int(blockIdx.x) % hb) / p.Hq;
     const int hk = h / (p.Hq / p.Hkv);
     const int n = qt + 1;                        // key tiles 0..qt
     const int q0 = qt * 128;
@@ -111,7 +124,7 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
         }
-        mbar_init(p_full, 4); mbar_init(o_full, 1); mbar_init(o_empty, 4);
+        mbar_init(p_full, 4); mbar_init(o_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -125,16 +138,16 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             mbar_arrive_expect_tx(q_full, TB);
-            load_tile<HD>(smem + OFF_Q, &p.tmQ, q_full, h * HD, b * p.T + q0);
+            load_tile<HD>(smem + OFF_Q, 16384, &p.tmQ, q_full, h * HD, b * p.T + q0);
             for (int j = 0; j < n; j++) {
                 const int st = j & 1;
                 const uint32_t ph = (j >> 1) & 1;
                 ATT_WAIT(&k_empty[st], ph ^ 1u, DS_TIMEOUT_PRODUCER);
                 mbar_arrive_expect_tx(&k_full[st], TB);
-                load_tile<HD>(smem + OFF_K + st * TB, &p.tmK, &k_full[st], hk * HD, b * p.T + j * 128);
+                load_tile<HD>(smem + OFF_K + st * TB, 16384, &p.tmK, &k_full[st], hk * HD, b * p.T + j * 128);
                 ATT_WAIT(&v_empty[st], ph ^ 1u, DS_TIMEOUT_PRODUCER);
                 mbar_arrive_expect_tx(&v_full[st], TB);
-                load_tile<HD>(smem + OFF_V + st * TB, &p.tmV, &v_full[st], hk * HD, b * p.T + j * 128);
+                load_tile<HD>(smem + OFF_V + st * TB, 16384, &p.tmV, &v_full[st], hk * HD, b * p.T + j * 128);
             }
         }
     } else if (warp == 1) {
@@ -149,17 +162,16 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
                     ATT_WAIT(&k_full[st], ph, DS_TIMEOUT_MMA);
                     ATT_WAIT(&s_empty[st], ph ^ 1u, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kk<HD>(tmem + st * 128, sQ, sK + st * TB, false);
+                    mma_kk<HD, 128>(tmem + st * 128, sQ, 16384, sK + st * TB, 16384, false);
                     umma_commit(&k_empty[st]);
                     umma_commit(&s_full[st]);
                 }
-                if (j >= 0) {
+                if (j >= 0) {      // O += P_j . V_j once the softmax warps have published P_j (and rescaled O)
                     const int st = j & 1;
                     ATT_WAIT(&v_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
                     ATT_WAIT(p_full, j & 1, DS_TIMEOUT_MMA);
-                    ATT_WAIT(o_empty, (j & 1) ^ 1u, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kmn<HD>(TM_O, sP, sV + st * TB, false);
+                    mma_kmn<HD, 128>(TM_O, sP, sV + st * TB, 16384, j > 0);
                     umma_commit(&v_empty[st]);
                     umma_commit(o_full);
                 }
@@ -171,9 +183,6 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
         const int q_idx = q0 + row;
         const uint32_t lane_addr = uint32_t(lg * 32) << 16;
         float m = -INFINITY, l = 0.f;
-        float o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; i++) o[i] = 0.f;
         uint8_t* sP = smem + OFF_P;
 
         for (int j = 0; j < n; j++) {
@@ -182,65 +191,69 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
             tcgen05_fence_after_sync();
             const bool diag = (j == qt);
             const uint32_t ts = tmem + st * 128 + lane_addr;
-            float mx = m;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t r[32];
-                tmem_ld_x32(ts + c * 32, r);
-                tmem_ld_wait();
+            uint32_t s[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; c++) tmem_ld_x32(ts + c * 32, s[c]);
+            tmem_ld_wait();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[st]);   // the scores are in registers: S buffer is free
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
-                    float s = __uint_as_float(r[i]) * p.scale_log2;
-                    if (diag && (j * 128 + c * 32 + i > q_idx)) s = -INFINITY;
-                    mx = fmaxf(mx, s);
+                    float v = __uint_as_float(s[c][i]) * p.scale_log2;
+                    if (diag && (j * 128 + c * 32 + i > q_idx)) v = -INFINITY;
+                    s[c][i] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
                 }
+            float alpha = 1.f;
+            bool rescale = false;
+            if (j == 0) {
+                m = mx;
+            } else if (mx > m + kRescaleThreshold) {
+                alpha = ex2_approx(m - mx);
+                m = mx;
+                rescale = true;
             }
-            const float alpha = exp2f(m - mx);   // m = -inf on the first tile -> 0
-            if (j > 0) {
-                ATT_WAIT(o_full, (j - 1) & 1, DS_TIMEOUT_SOFTMAX);
-                tcgen05_fence_after_sync();
-#pragma unroll
-                for (int c = 0; c < HD / 32; c++) {
-                    uint32_t r[32];
-                    tmem_ld_x32(TM_O + lane_addr + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * alpha;
-                }
-                tcgen05_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(o_empty);
-            }
-            l *= alpha;
+            uint32_t pk[64];
             float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t r[32];
-                tmem_ld_x32(ts + c * 32, r);
-                tmem_ld_wait();
-                uint32_t pk[16];
+#pragma unroll
+            for (int c = 0; c < 4; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float s0 = __uint_as_float(r[i]) * p.scale_log2, s1 = __uint_as_float(r[i + 1]) * p.scale_log2;
-                    float p0 = exp2f(s0 - mx), p1 = exp2f(s1 - mx);
-                    if (diag) {
-                        if (j * 128 + c * 32 + i > q_idx) p0 = 0.f;
-                        if (j * 128 + c * 32 + i + 1 > q_idx) p1 = 0.f;
-                    }
+                    const float p0 = ex2_approx(__uint_as_float(s[c][i]) - m);
+                    const float p1 = ex2_approx(__uint_as_float(s[c][i + 1]) - m);
                     sum += p0 + p1;
-                    pk[i >> 1] = pack_bf16x2(p0, p1);
+                    pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
                 }
+            if (j > 0) {
+                // P buffer and O are only safe to touch once the previous P.V has completed
+                ATT_WAIT(o_full, (j - 1) & 1, DS_TIMEOUT_SOFTMAX);
+                tcgen05_fence_after_sync();
+                if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; c++) {
+                        uint32_t r[32];
+                        tmem_ld_x32(TM_O + lane_addr + c * 32, r);
+                        tmem_ld_wait();
 #pragma unroll
-                for (int g = 0; g < 4; g++)
-                    *reinterpret_cast<uint4*>(sP + kmajor_off(row, c * 32 + g * 8)) =
-                        make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                        for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st_x32(TM_O + lane_addr + c * 32, r);
+                    }
+                    tmem_st_wait();
+                }
             }
-            l += sum;
-            m = mx;
+            l = l * alpha + sum;
+#pragma unroll
+            for (int g = 0; g < 16; g++)
+                *reinterpret_cast<uint4*>(sP + kmajor_off(row, g * 8)) =
+                    make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&s_empty[st]); mbar_arrive(p_full); }
+            if (lane == 0) mbar_arrive(p_full);
         }
         ATT_WAIT(o_full, (n - 1) & 1, DS_TIMEOUT_SOFTMAX);
         tcgen05_fence_after_sync();
@@ -257,11 +270,8 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
                 for (int g = 0; g < 4; g++) {
                     uint32_t w[4];
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int e = c * 32 + g * 8 + i * 2;
-                        w[i] = pack_bf16x2((o[e] + __uint_as_float(r[g * 8 + i * 2])) * inv_l,
-                                           (o[e + 1] + __uint_as_float(r[g * 8 + i * 2 + 1])) * inv_l);
-                    }
+                    for (int i = 0; i < 4; i++)
+                        w[i] = pack_bf16x2(__uint_as_float(r[g * 8 + i * 2]) * inv_l, __uint_as_float(r[g * 8 + i * 2 + 1]) * inv_l);
                     *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
@@ -304,30 +314,38 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __
 }
 
 // ─────────────────────────────── backward: dQ ───────────────────────────────
+// CTA = 128 query rows of one head; keys are walked in sub-tiles of 64 so that S and dP can be double
+// buffered in TMEM: S[2] at columns [0,128), dP[2] at [128,256), dQ accumulator at [256, 256+HD).
 
 template <int HD>
 __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
-    constexpr uint32_t TB = Tile<HD>::BYTES;
-    constexpr uint32_t OFF_Q = 0, OFF_DO = TB, OFF_K = 2 * TB, OFF_V = 4 * TB, OFF_DS = 6 * TB, OFF_BAR = 6 * TB + 32768;
+    constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
+    constexpr uint32_t OFF_Q = 0, OFF_DO = TB, OFF_K = 2 * TB, OFF_V = 2 * TB + 2 * TB64, OFF_DS = 2 * TB + 4 * TB64,
+                       OFF_BAR = OFF_DS + 32768;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-    uint64_t *qdo_full = bars, *kv_full = bars + 1, *kv_empty = bars + 3, *s_full = bars + 5, *s_empty = bars + 6,
-             *ds_full = bars + 7, *dq_full = bars + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint64_t *qdo_full = bars, *kv_full = bars + 1, *kv_empty = bars + 3, *s_full = bars + 5, *s_empty = bars + 7,
+             *ds_full = bars + 9, *ds_empty = bars + 11, *dq_full = bars + 13;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = gridDim.x - 1 - blockIdx.x;
-    const int h = blockIdx.y, b = blockIdx.z;
+    const int nt = (p.T + 127) / 128, hb = p.Hq * p.B;
+    const int qt = nt - 1 - int(blockIdx.x) / hb;   // heavy-first over the whole launch
+    const int h = (int(blockIdx.x) % hb) % p.Hq, b = (int(blockIdx.x) % hb) / p.Hq;
     const int hk = h / (p.Hq / p.Hkv);
-    const int n = qt + 1;
+    const int n = 2 * (qt + 1);    // key sub-tiles of 64 rows: 0 .. 2*qt+1
     const int q0 = qt * 128;
 
     if (threadIdx.x == 0) {
         mbar_init(qdo_full, 1);
-        for (int i = 0; i < 2; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-        mbar_init(s_full, 1); mbar_init(s_empty, 4); mbar_init(ds_full, 4); mbar_init(dq_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+            mbar_init(&ds_full[i], 4); mbar_init(&ds_empty[i], 1);
+        }
+        mbar_init(dq_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -341,14 +359,14 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             mbar_arrive_expect_tx(qdo_full, 2 * TB);
-            load_tile<HD>(smem + OFF_Q, &p.tmQ, qdo_full, h * HD, b * p.T + q0);
-            load_tile<HD>(smem + OFF_DO, &p.tmdO, qdo_full, h * HD, b * p.T + q0);
+            load_tile<HD>(smem + OFF_Q, 16384, &p.tmQ, qdo_full, h * HD, b * p.T + q0);
+            load_tile<HD>(smem + OFF_DO, 16384, &p.tmdO, qdo_full, h * HD, b * p.T + q0);
             for (int j = 0; j < n; j++) {
                 const int st = j & 1;
                 ATT_WAIT(&kv_empty[st], ((j >> 1) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
-                mbar_arrive_expect_tx(&kv_full[st], 2 * TB);
-                load_tile<HD>(smem + OFF_K + st * TB, &p.tmK, &kv_full[st], hk * HD, b * p.T + j * 128);
-                load_tile<HD>(smem + OFF_V + st * TB, &p.tmV, &kv_full[st], hk * HD, b * p.T + j * 128);
+                mbar_arrive_expect_tx(&kv_full[st], 2 * TB64);
+                load_tile<HD>(smem + OFF_K + st * TB64, 8192, &p.tmK64, &kv_full[st], hk * HD, b * p.T + j * 64);
+                load_tile<HD>(smem + OFF_V + st * TB64, 8192, &p.tmV64, &kv_full[st], hk * HD, b * p.T + j * 64);
             }
         }
     } else if (warp == 1) {
@@ -356,18 +374,25 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
             const uint32_t sQ = smem_u32(smem + OFF_Q), sDO = smem_u32(smem + OFF_DO), sK = smem_u32(smem + OFF_K),
                            sV = smem_u32(smem + OFF_V), sDS = smem_u32(smem + OFF_DS);
             ATT_WAIT(qdo_full, 0, DS_TIMEOUT_MMA);
-            for (int j = 0; j < n; j++) {
-                const int st = j & 1;
-                ATT_WAIT(&kv_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
-                ATT_WAIT(s_empty, (j & 1) ^ 1u, DS_TIMEOUT_MMA);
-                tcgen05_fence_after_sync();
-                mma_kk<HD>(TM_S, sQ, sK + st * TB, false);
-                mma_kk<HD>(TM_DP, sDO, sV + st * TB, false);
-                umma_commit(s_full);
-                ATT_WAIT(ds_full, j & 1, DS_TIMEOUT_MMA);
-                tcgen05_fence_after_sync();
-                mma_kmn<HD>(TM_DQ, sDS, sK + st * TB, j > 0);
-                umma_commit(&kv_empty[st]);
+            for (int j = -1; j < n; j++) {
+                if (j + 1 < n) {
+                    const int jn = j + 1, st = jn & 1;
+                    const uint32_t ph = (jn >> 1) & 1;
+                    ATT_WAIT(&kv_full[st], ph, DS_TIMEOUT_MMA);
+                    ATT_WAIT(&s_empty[st], ph ^ 1u, DS_TIMEOUT_MMA);
+                    tcgen05_fence_after_sync();
+                    mma_kk<HD, 64>(TM_S + st * 64, sQ, 16384, sK + st * TB64, 8192, false);
+                    mma_kk<HD, 64>(TM_DP + st * 64, sDO, 16384, sV + st * TB64, 8192, false);
+                    umma_commit(&s_full[st]);
+                }
+                if (j >= 0) {
+                    const int st = j & 1;
+                    ATT_WAIT(&ds_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
+                    tcgen05_fence_after_sync();
+                    mma_kmn<HD, 64>(TM_DQ, sDS + st * 16384, sK + st * TB64, 8192, j > 0);
+                    umma_commit(&kv_empty[st]);
+                    umma_commit(&ds_empty[st]);
+                }
             }
             umma_commit(dq_full);
         }
@@ -380,38 +405,46 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
         const size_t stat = (size_t(b) * p.Hq + h) * p.T + q_idx;
         const float lse2 = ok ? p.lse[stat] * kLog2e : INFINITY;
         const float dlt = ok ? p.delta[stat] : 0.f;
-        uint8_t* sDS = smem + OFF_DS;
         for (int j = 0; j < n; j++) {
-            ATT_WAIT(s_full, j & 1, DS_TIMEOUT_SOFTMAX);
+            const int st = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            ATT_WAIT(&s_full[st], ph, DS_TIMEOUT_SOFTMAX);
             tcgen05_fence_after_sync();
-            const bool diag = (j == qt);
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t rs[32], rp[32];
-                tmem_ld_x32(TM_S + lane_addr + c * 32, rs);
-                tmem_ld_x32(TM_DP + lane_addr + c * 32, rp);
-                tmem_ld_wait();
-                uint32_t pk[16];
+            uint32_t rs[2][32], rp[2][32];
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                tmem_ld_x32(TM_S + st * 64 + lane_addr + c * 32, rs[c]);
+                tmem_ld_x32(TM_DP + st * 64 + lane_addr + c * 32, rp[c]);
+            }
+            tmem_ld_wait();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[st]);
+            const bool diag = (j * 64 + 63 > q0);
+            uint32_t pk[32];
+#pragma unroll
+            for (int c = 0; c < 2; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2);
-                    float p1 = exp2f(__uint_as_float(rs[i + 1]) * p.scale_log2 - lse2);
+                    float p0 = ex2_approx(__uint_as_float(rs[c][i]) * p.scale_log2 - lse2);
+                    float p1 = ex2_approx(__uint_as_float(rs[c][i + 1]) * p.scale_log2 - lse2);
                     if (diag) {
-                        if (j * 128 + c * 32 + i > q_idx) p0 = 0.f;
-                        if (j * 128 + c * 32 + i + 1 > q_idx) p1 = 0.f;
+                        if (j * 64 + c * 32 + i > q_idx) p0 = 0.f;
+                        if (j * 64 + c * 32 + i + 1 > q_idx) p1 = 0.f;
                     }
-                    pk[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(rp[i]) - dlt) * p.scale,
-                                             p1 * (__uint_as_float(rp[i + 1]) - dlt) * p.scale);
+                    pk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * (__uint_as_float(rp[c][i]) - dlt) * p.scale,
+                                                        p1 * (__uint_as_float(rp[c][i + 1]) - dlt) * p.scale);
                 }
+            ATT_WAIT(&ds_empty[st], ph ^ 1u, DS_TIMEOUT_SOFTMAX);
+            uint8_t* sDS = smem + OFF_DS + st * 16384;
 #pragma unroll
-                for (int g = 0; g < 4; g++)
-                    *reinterpret_cast<uint4*>(sDS + kmajor_off(row, c * 32 + g * 8)) =
-                        make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-            }
+            for (int g = 0; g < 8; g++)
+                *reinterpret_cast<uint4*>(sDS + kmajor_off(row, g * 8)) =
+                    make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(s_empty); mbar_arrive(ds_full); }
+            if (lane == 0) mbar_arrive(&ds_full[st]);
         }
         ATT_WAIT(dq_full, 0, DS_TIMEOUT_SOFTMAX);
         tcgen05_fence_after_sync();
@@ -442,34 +475,40 @@ done:
 }
 
 // ─────────────────────────────── backward: dK, dV ───────────────────────────────
+// CTA = 128 key rows of one KV head; queries are walked in sub-tiles of 64 rows over all query heads of
+// the group.  TMEM: S^T[2] at [0,128), dP^T[2] at [128,256), dV at [256,256+HD), dK at [256+HD,256+2HD).
 
 template <int HD>
 __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
-    constexpr uint32_t TB = Tile<HD>::BYTES;
-    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 3 * TB, OFF_PT = 4 * TB, OFF_DST = 4 * TB + 32768,
-                       OFF_STAT = 4 * TB + 65536, OFF_BAR = OFF_STAT + 2048;
+    constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
+    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + 2 * TB64, OFF_PT = 2 * TB + 4 * TB64,
+                       OFF_DST = OFF_PT + 32768, OFF_STAT = OFF_DST + 32768, OFF_BAR = OFF_STAT + 1024;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-    uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 2, *s_full = bars + 3, *s_empty = bars + 4,
-             *p_full = bars + 5, *acc_full = bars + 6, *stat_full = bars + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 3, *s_full = bars + 5, *s_empty = bars + 7,
+             *p_full = bars + 9, *p_empty = bars + 11, *acc_full = bars + 13, *stat_full = bars + 14;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* stat = reinterpret_cast<float*>(smem + OFF_STAT);   // [2 buffers][lse2 128 | delta 128]
+    float* stat = reinterpret_cast<float*>(smem + OFF_STAT);   // [2 buffers][lse2 64 | delta 64]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kt = blockIdx.x;   // key tile; tile 0 has the most work and starts first
-    const int hk = blockIdx.y, b = blockIdx.z;
+    const int hbk = p.Hkv * p.B;
+    const int kt = int(blockIdx.x) / hbk;   // key tile 0 has the most work: all its CTAs start first
+    const int hk = (int(blockIdx.x) % hbk) % p.Hkv, b = (int(blockIdx.x) % hbk) / p.Hkv;
     const int G = p.Hq / p.Hkv;
-    const int nq = (p.T + 127) / 128;
-    const int per_head = nq - kt;
+    const int nq64 = (p.T + 63) / 64;
+    const int per_head = nq64 - 2 * kt;      // query sub-tiles 2*kt .. nq64-1 can see these keys
     const int iters = G * per_head;
     const int kv0 = kt * 128;
 
     if (threadIdx.x == 0) {
-        mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1);
-        mbar_init(s_full, 1); mbar_init(s_empty, 4); mbar_init(p_full, 4); mbar_init(acc_full, 1);
-        mbar_init(stat_full, 128);
+        mbar_init(kv_full, 1); mbar_init(acc_full, 1); mbar_init(stat_full, 128);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+            mbar_init(&p_full[i], 4); mbar_init(&p_empty[i], 1);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -483,14 +522,14 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
     if (warp == 0) {
         if (lane == 0) {
             mbar_arrive_expect_tx(kv_full, 2 * TB);
-            load_tile<HD>(smem + OFF_K, &p.tmK, kv_full, hk * HD, b * p.T + kv0);
-            load_tile<HD>(smem + OFF_V, &p.tmV, kv_full, hk * HD, b * p.T + kv0);
+            load_tile<HD>(smem + OFF_K, 16384, &p.tmK, kv_full, hk * HD, b * p.T + kv0);
+            load_tile<HD>(smem + OFF_V, 16384, &p.tmV, kv_full, hk * HD, b * p.T + kv0);
             for (int it = 0; it < iters; it++) {
-                const int h = hk * G + it / per_head, qi = kt + it % per_head;
-                ATT_WAIT(qdo_empty, (it & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
-                mbar_arrive_expect_tx(qdo_full, 2 * TB);
-                load_tile<HD>(smem + OFF_Q, &p.tmQ, qdo_full, h * HD, b * p.T + qi * 128);
-                load_tile<HD>(smem + OFF_DO, &p.tmdO, qdo_full, h * HD, b * p.T + qi * 128);
+                const int h = hk * G + it / per_head, qs = 2 * kt + it % per_head, st = it & 1;
+                ATT_WAIT(&qdo_empty[st], ((it >> 1) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
+                mbar_arrive_expect_tx(&qdo_full[st], 2 * TB64);
+                load_tile<HD>(smem + OFF_Q + st * TB64, 8192, &p.tmQ64, &qdo_full[st], h * HD, b * p.T + qs * 64);
+                load_tile<HD>(smem + OFF_DO + st * TB64, 8192, &p.tmdO64, &qdo_full[st], h * HD, b * p.T + qs * 64);
             }
         }
     } else if (warp == 1) {
@@ -498,18 +537,26 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
             const uint32_t sK = smem_u32(smem + OFF_K), sV = smem_u32(smem + OFF_V), sQ = smem_u32(smem + OFF_Q),
                            sDO = smem_u32(smem + OFF_DO), sPT = smem_u32(smem + OFF_PT), sDST = smem_u32(smem + OFF_DST);
             ATT_WAIT(kv_full, 0, DS_TIMEOUT_MMA);
-            for (int it = 0; it < iters; it++) {
-                ATT_WAIT(qdo_full, it & 1, DS_TIMEOUT_MMA);
-                ATT_WAIT(s_empty, (it & 1) ^ 1u, DS_TIMEOUT_MMA);
-                tcgen05_fence_after_sync();
-                mma_kk<HD>(TM_ST, sK, sQ, false);     // S^T  = K . Q^T
-                mma_kk<HD>(TM_DPT, sV, sDO, false);   // dP^T = V . dO^T
-                umma_commit(s_full);
-                ATT_WAIT(p_full, it & 1, DS_TIMEOUT_MMA);
-                tcgen05_fence_after_sync();
-                mma_kmn<HD>(TM_DV, sPT, sDO, it > 0);   // dV += P^T . dO
-                mma_kmn<HD>(TM_DK, sDST, sQ, it > 0);   // dK += dS^T . Q
-                umma_commit(qdo_empty);
+            for (int it = -1; it < iters; it++) {
+                if (it + 1 < iters) {
+                    const int in = it + 1, st = in & 1;
+                    const uint32_t ph = (in >> 1) & 1;
+                    ATT_WAIT(&qdo_full[st], ph, DS_TIMEOUT_MMA);
+                    ATT_WAIT(&s_empty[st], ph ^ 1u, DS_TIMEOUT_MMA);
+                    tcgen05_fence_after_sync();
+                    mma_kk<HD, 64>(TM_ST + st * 64, sK, 16384, sQ + st * TB64, 8192, false);     // S^T  = K . Q^T
+                    mma_kk<HD, 64>(TM_DPT + st * 64, sV, 16384, sDO + st * TB64, 8192, false);   // dP^T = V . dO^T
+                    umma_commit(&s_full[st]);
+                }
+                if (it >= 0) {
+                    const int st = it & 1;
+                    ATT_WAIT(&p_full[st], (it >> 1) & 1, DS_TIMEOUT_MMA);
+                    tcgen05_fence_after_sync();
+                    mma_kmn<HD, 64>(TM_DV, sPT + st * 16384, sDO + st * TB64, 8192, it > 0);    // dV += P^T . dO
+                    mma_kmn<HD, 64>(TM_DK, sDST + st * 16384, sQ + st * TB64, 8192, it > 0);    // dK += dS^T . Q
+                    umma_commit(&qdo_empty[st]);
+                    umma_commit(&p_empty[st]);
+                }
             }
             umma_commit(acc_full);
         }
@@ -519,55 +566,71 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
         const int tid = threadIdx.x - 64;   // 0..127 among the compute threads
         const int kv_idx = kv0 + row;
         const uint32_t lane_addr = uint32_t(lg * 32) << 16;
-        uint8_t* sPT = smem + OFF_PT;
-        uint8_t* sDST = smem + OFF_DST;
-        for (int it = 0; it < iters; it++) {
-            const int h = hk * G + it / per_head, qi = kt + it % per_head;
-            float* lse2 = stat + (it & 1) * 256;
-            float* dlt = lse2 + 128;
-            {
-                const int q = qi * 128 + tid;
-                const bool okq = q < p.T;
-                const size_t si = (size_t(b) * p.Hq + h) * p.T + q;
-                lse2[tid] = okq ? p.lse[si] * kLog2e : INFINITY;   // +inf -> probability 0 for padded queries
-                dlt[tid] = okq ? p.delta[si] : 0.f;
+        // per-query statistics are fetched one iteration ahead so their global-memory latency hides
+        // behind the element-wise work of the current iteration
+        auto fetch = [&](int it, float& fl, float& fd) {
+            fl = INFINITY; fd = 0.f;   // +inf -> probability 0 for padded queries
+            if (tid < 64 && it < iters) {
+                const int h = hk * G + it / per_head, q = (2 * kt + it % per_head) * 64 + tid;
+                if (q < p.T) {
+                    const size_t si = (size_t(b) * p.Hq + h) * p.T + q;
+                    fl = p.lse[si] * kLog2e; fd = p.delta[si];
+                }
             }
-            mbar_arrive(stat_full);   // all 128 rows of lse / delta are in shared memory after this phase
+        };
+        float next_l, next_d;
+        fetch(0, next_l, next_d);
+        for (int it = 0; it < iters; it++) {
+            const int qs = 2 * kt + it % per_head, st = it & 1;
+            const uint32_t ph = (it >> 1) & 1;
+            float* lse2 = stat + st * 128;
+            float* dlt = lse2 + 64;
+            if (tid < 64) { lse2[tid] = next_l; dlt[tid] = next_d; }
+            fetch(it + 1, next_l, next_d);
+            mbar_arrive(stat_full);   // all 64 entries of lse / delta are in shared memory after this phase
             ATT_WAIT(stat_full, it & 1, DS_TIMEOUT_SOFTMAX);
-            ATT_WAIT(s_full, it & 1, DS_TIMEOUT_SOFTMAX);
+            ATT_WAIT(&s_full[st], ph, DS_TIMEOUT_SOFTMAX);
             tcgen05_fence_after_sync();
-            const bool diag = (qi == kt);
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t rs[32], rp[32];
-                tmem_ld_x32(TM_ST + lane_addr + c * 32, rs);
-                tmem_ld_x32(TM_DPT + lane_addr + c * 32, rp);
-                tmem_ld_wait();
-                uint32_t pk[16], dk[16];
+            uint32_t rs[2][32], rp[2][32];
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                tmem_ld_x32(TM_ST + st * 64 + lane_addr + c * 32, rs[c]);
+                tmem_ld_x32(TM_DPT + st * 64 + lane_addr + c * 32, rp[c]);
+            }
+            tmem_ld_wait();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[st]);
+            const bool diag = (qs * 64 < kv0 + 127);
+            uint32_t pk[32], dk[32];
+#pragma unroll
+            for (int c = 0; c < 2; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const int col = c * 32 + i;
-                    float p0 = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2[col]);
-                    float p1 = exp2f(__uint_as_float(rs[i + 1]) * p.scale_log2 - lse2[col + 1]);
+                    float p0 = ex2_approx(__uint_as_float(rs[c][i]) * p.scale_log2 - lse2[col]);
+                    float p1 = ex2_approx(__uint_as_float(rs[c][i + 1]) * p.scale_log2 - lse2[col + 1]);
                     if (diag) {
-                        if (kv_idx > qi * 128 + col) p0 = 0.f;
-                        if (kv_idx > qi * 128 + col + 1) p1 = 0.f;
+                        if (kv_idx > qs * 64 + col) p0 = 0.f;
+                        if (kv_idx > qs * 64 + col + 1) p1 = 0.f;
                     }
-                    pk[i >> 1] = pack_bf16x2(p0, p1);
-                    dk[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(rp[i]) - dlt[col]) * p.scale,
-                                             p1 * (__uint_as_float(rp[i + 1]) - dlt[col + 1]) * p.scale);
+                    pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+                    dk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * (__uint_as_float(rp[c][i]) - dlt[col]) * p.scale,
+                                                        p1 * (__uint_as_float(rp[c][i + 1]) - dlt[col + 1]) * p.scale);
                 }
+            ATT_WAIT(&p_empty[st], ph ^ 1u, DS_TIMEOUT_SOFTMAX);
+            uint8_t* sPT = smem + OFF_PT + st * 16384;
+            uint8_t* sDST = smem + OFF_DST + st * 16384;
 #pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    const uint32_t off = kmajor_off(row, c * 32 + g * 8);
-                    *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-                    *reinterpret_cast<uint4*>(sDST + off) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
-                }
+            for (int g = 0; g < 8; g++) {
+                const uint32_t off = kmajor_off(row, g * 8);
+                *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                *reinterpret_cast<uint4*>(sDST + off) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
             }
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(s_empty); mbar_arrive(p_full); }
+            if (lane == 0) mbar_arrive(&p_full[st]);
         }
         ATT_WAIT(acc_full, 0, DS_TIMEOUT_SOFTMAX);
         tcgen05_fence_after_sync();
@@ -604,8 +667,8 @@ done:
 }
 
 template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 32768 + 256 + 1024; }
-template <int HD> constexpr size_t dq_smem()  { return 6 * Tile<HD>::BYTES + 32768 + 256 + 1024; }
-template <int HD> constexpr size_t dkv_smem() { return 4 * Tile<HD>::BYTES + 65536 + 2048 + 256 + 1024; }
+template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 4 * Tile<HD>::BYTES64 + 32768 + 256 + 1024; }
+template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 4 * Tile<HD>::BYTES64 + 65536 + 1024 + 256 + 1024; }
 
 int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const void* V, const void* dO, int B, int T,
               int Hq, int Hkv, int hd) {
@@ -614,7 +677,13 @@ int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const vo
     if ((rc = get_tmap_bf16(ctx, Q, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 128, &p.tmQ))) return rc;
     if ((rc = get_tmap_bf16(ctx, K, uint64_t(Hkv) * hd, rows, uint64_t(Hkv) * hd * 2, 64, 128, &p.tmK))) return rc;
     if ((rc = get_tmap_bf16(ctx, V, uint64_t(Hkv) * hd, rows, uint64_t(Hkv) * hd * 2, 64, 128, &p.tmV))) return rc;
-    if (dO && (rc = get_tmap_bf16(ctx, dO, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 128, &p.tmdO))) return rc;
+    if (dO) {
+        if ((rc = get_tmap_bf16(ctx, dO, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 128, &p.tmdO))) return rc;
+        if ((rc = get_tmap_bf16(ctx, dO, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 64, &p.tmdO64))) return rc;
+        if ((rc = get_tmap_bf16(ctx, Q, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 64, &p.tmQ64))) return rc;
+        if ((rc = get_tmap_bf16(ctx, K, uint64_t(Hkv) * hd, rows, uint64_t(Hkv) * hd * 2, 64, 64, &p.tmK64))) return rc;
+        if ((rc = get_tmap_bf16(ctx, V, uint64_t(Hkv) * hd, rows, uint64_t(Hkv) * hd * 2, 64, 64, &p.tmV64))) return rc;
+    }
     return TA_OK;
 }
 
@@ -647,7 +716,7 @@ int ta_flash_attn_fwd(ta_ctx* ctx, const void* Q, const void* K, const void* V, 
     p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse;
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
     p.scale = 1.f / std::sqrt(float(head_dim)); p.scale_log2 = p.scale * kLog2e; p.status = ctx->d_status;
-    const dim3 grid((T + 127) / 128, Hq, B);
+    const dim3 grid(((T + 127) / 128) * Hq * B);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // causal: half the square, two contractions (S, P.V)
     ProfScope prof(ctx, s, PROF_ATTN_FWD, 2.0 * 2.0 * B * Hq * double(T) * T * head_dim * 0.5);
@@ -694,16 +763,16 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
     ProfScope prof(ctx, s, PROF_ATTN_BWD, 5.0 * 2.0 * B * Hq * double(T) * T * head_dim * 0.5);
     if (head_dim == 128) {
         if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<128>, dkv_smem<128>())) return rc;
-        attn_bwd_dkv_kernel<128><<<dim3(nt, Hkv, B), 192, dkv_smem<128>(), s>>>(p);
+        attn_bwd_dkv_kernel<128><<<dim3(nt * Hkv * B), 192, dkv_smem<128>(), s>>>(p);
         TA_LAUNCH_CHECK(ctx, "attn_bwd_dkv_kernel");
         if (int rc = set_smem(ctx, attn_bwd_dq_kernel<128>, dq_smem<128>())) return rc;
-        attn_bwd_dq_kernel<128><<<dim3(nt, Hq, B), 192, dq_smem<128>(), s>>>(p);
+        attn_bwd_dq_kernel<128><<<dim3(nt * Hq * B), 192, dq_smem<128>(), s>>>(p);
     } else {
         if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<64>, dkv_smem<64>())) return rc;
-        attn_bwd_dkv_kernel<64><<<dim3(nt, Hkv, B), 192, dkv_smem<64>(), s>>>(p);
+        attn_bwd_dkv_kernel<64><<<dim3(nt * Hkv * B), 192, dkv_smem<64>(), s>>>(p);
         TA_LAUNCH_CHECK(ctx, "attn_bwd_dkv_kernel");
         if (int rc = set_smem(ctx, attn_bwd_dq_kernel<64>, dq_smem<64>())) return rc;
-        attn_bwd_dq_kernel<64><<<dim3(nt, Hq, B), 192, dq_smem<64>(), s>>>(p);
+        attn_bwd_dq_kernel<64><<<dim3(nt * Hq * B), 192, dq_smem<64>(), s>>>(p);
     }
     TA_LAUNCH_CHECK(ctx, "attn_bwd_dq_kernel");
     return TA_OK;
