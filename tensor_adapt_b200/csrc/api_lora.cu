@@ -23,7 +23,7 @@ int lora_down(ta_ctx* ctx, cudaStream_t s, const __nv_bfloat16* x, int BT, int i
 size_t lora_fwd_scratch_bytes(int BT, int r) { return align256(size_t(BT) * r * 2); }
 size_t lora_bwd_scratch_bytes(const ta_ctx* ctx, int BT, int in, int out, int r) {
     return 2 * align256(size_t(BT) * r * 2) +
-           align256(std::max(tokens_gemm_ws_bytes(ctx, out, r, BT), tokens_gemm_ws_bytes(ctx, in, r, BT)));
+           align256(std::max(tokens_gemm_ws_bytes_max(ctx, out, r), tokens_gemm_ws_bytes_max(ctx, in, r)));
 }
 
 }  // namespace ta

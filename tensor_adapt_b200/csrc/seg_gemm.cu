@@ -37,17 +37,24 @@ struct alignas(64) SegGemmParams {
     int* status;
 };
 
-constexpr int BM = 128;
+constexpr int BM = 128;       // rows of one MMA / one TMEM accumulator
 constexpr int BK = 64;
 constexpr int GROUP_M = 16;   // m-tiles per raster group: a wave touches ~16 A tiles and ~9 B tiles -> L2 reuse
 
-template <int BN>
+constexpr uint32_t pow2_at_least(uint32_t v) { uint32_t p = 32; while (p < v) p <<= 1; return p; }
+
+// MH = number of 128-row accumulators per CTA tile.  MH = 1: tile 128 x BN, accumulator double-buffered
+// in TMEM so the epilogue overlaps the next main loop.  MH = 2: tile 256 x BN with two accumulators that
+// share every B tile: a third less operand traffic per FLOP (the 128-row kernel is bound by operand
+// delivery, not by the tensor pipe), at the price of a non-overlapped epilogue.
+template <int BN, int MH>
 struct Cfg {
-    static constexpr uint32_t A_BYTES = BM * BK * 2;
-    static constexpr uint32_t B_BYTES = (BN < 64 ? 64 : BN) * BK * 2;
+    static constexpr int TILE_M = BM * MH;
+    static constexpr uint32_t A_BYTES = TILE_M * BK * 2;
+    static constexpr uint32_t B_BYTES = (BN < 64 ? 64 : (BN + 63) / 64 * 64) * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
-    static constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+    static constexpr int STAGES = MH == 2 ? 3 : (BN >= 224) ? 4 : (BN == 128) ? 6 : 8;
+    static constexpr uint32_t TMEM_COLS = MH == 2 ? 512 : pow2_at_least(2 * BN);
     static constexpr int NCHUNK_B = (BN + 63) / 64;
     static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
 };
@@ -56,7 +63,7 @@ struct TileCoord {
     int m0, n0, split;
 };
 
-__device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_tiles, int bn) {
+__device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_tiles, int bm, int bn) {
     const int per_split = m_tiles * n_tiles;
     TileCoord t;
     t.split = tile / per_split;
@@ -66,14 +73,14 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
     const int first_m = g * GROUP_M;
     const int gsz = min(GROUP_M, m_tiles - first_m);
     const int in_g = rem - g * per_group;
-    t.m0 = (first_m + in_g % gsz) * BM;
+    t.m0 = (first_m + in_g % gsz) * bm;
     t.n0 = (in_g / gsz) * bn;
     return t;
 }
 
-template <int BN>
+template <int BN, int MH>
 __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant__ SegGemmParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, MH>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -107,7 +114,7 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int m_tiles = (p.M + BM - 1) / BM;
+    const int m_tiles = (p.M + C::TILE_M - 1) / C::TILE_M;
     const int n_tiles = (p.N + BN - 1) / BN;
     const int total = m_tiles * n_tiles * p.split_k;
 
@@ -119,7 +126,7 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
             }
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, BN);
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, BN);
                 for (int s = 0; s < p.nseg; s++) {
                     const int nkb = (p.K[s] + BK - 1) / BK;
                     int kb_lo = 0, kb_hi = nkb;
@@ -137,8 +144,8 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
                         uint8_t* sb = sa + C::A_BYTES;
                         mbar_arrive_expect_tx(&full[stage], tx);
                         if (!a_mn) {
-                            tma_load_2d(sa, &p.tmA[s], &full[stage], kb * BK, tc.m0);
-                        } else {
+                            tma_load_2d(sa, &p.tmA[s], &full[stage], kb * BK, tc.m0);   // box {64, 128*MH}
+                        } else {                                                        // MH == 1 only (host)
                             tma_load_2d(sa, &p.tmA[s], &full[stage], tc.m0, kb * BK);
                             tma_load_2d(sa + 8192, &p.tmA[s], &full[stage], tc.m0 + 64, kb * BK);
                         }
@@ -157,11 +164,12 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0, lt = 0;
             for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, BN);
-                const uint32_t buf = lt & 1u, use = lt >> 1;
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, BN);
+                const uint32_t buf = MH == 2 ? 0u : (lt & 1u);
+                const uint32_t use = MH == 2 ? lt : (lt >> 1);
                 if (!mbar_wait(&tempty[buf], (use & 1u) ^ 1u, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
                 tcgen05_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t d_tmem = tmem_base + (MH == 2 ? 0u : buf * BN);
                 uint32_t acc = 0;
                 for (int s = 0; s < p.nseg; s++) {
                     const int nkb = (p.K[s] + BK - 1) / BK;
@@ -182,11 +190,14 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
                         const int krem = p.K[s] - kb * BK;
                         const int kinstr = krem >= BK ? 4 : (krem + 15) / 16;
                         for (int ki = 0; ki < kinstr; ki++) {
-                            const uint64_t ad = a_mn ? smem_desc_sw128(sa + ki * 2048, 8192, 1024)
-                                                     : smem_desc_sw128(sa + ki * 32, 16, 1024);
                             const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
                                                      : smem_desc_sw128(sb + ki * 32, 16, 1024);
-                            umma_bf16(d_tmem, ad, bd, idesc, acc);
+#pragma unroll
+                            for (int hh = 0; hh < MH; hh++) {
+                                const uint64_t ad = a_mn ? smem_desc_sw128(sa + ki * 2048, 8192, 1024)
+                                                         : smem_desc_sw128(sa + hh * 16384 + ki * 32, 16, 1024);
+                                umma_bf16(d_tmem + hh * 256, ad, bd, idesc, acc);
+                            }
                             acc = 1;
                         }
                         umma_commit(&empty[stage]);
@@ -199,82 +210,86 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
         const int lg = warp & 3;   // TMEM lane group this warp may access
         uint32_t lt = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
-            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, BN);
-            const uint32_t buf = lt & 1u, use = lt >> 1;
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, BN);
+            const uint32_t buf = MH == 2 ? 0u : (lt & 1u);
+            const uint32_t use = MH == 2 ? lt : (lt >> 1);
             if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
             tcgen05_fence_after_sync();
-            const int row = tc.m0 + lg * 32 + lane;
-            const bool row_ok = row < p.M;
-            const uint32_t taddr = tmem_base + buf * BN + (uint32_t(lg * 32) << 16);
             constexpr int CW = BN >= 32 ? 32 : 16;
 #pragma unroll 1
-            for (int c = 0; c < BN / CW; c++) {
-                const int col0 = tc.n0 + c * CW;
-                if (col0 >= p.N) break;
-                float v[CW];
-                if constexpr (CW == 32) {
-                    uint32_t r[32];
-                    tmem_ld_x32(taddr + c * CW, r);
-                    tmem_ld_wait();
+            for (int hh = 0; hh < MH; hh++) {
+                const int row = tc.m0 + hh * BM + lg * 32 + lane;
+                const bool row_ok = row < p.M;
+                const uint32_t taddr = tmem_base + (MH == 2 ? uint32_t(hh) * 256u : buf * BN) + (uint32_t(lg * 32) << 16);
+#pragma unroll 1
+                for (int c = 0; c < BN / CW; c++) {
+                    const int col0 = tc.n0 + c * CW;
+                    if (col0 >= p.N) break;
+                    float v[CW];
+                    if constexpr (CW == 32) {
+                        uint32_t r[32];
+                        tmem_ld_x32(taddr + c * CW, r);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
-                } else {
-                    uint32_t r[16];
-                    tmem_ld_x16(taddr + c * CW, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-                }
-                if (!row_ok) continue;
-#pragma unroll
-                for (int g = 0; g < CW / 8; g++) {
-                    const int col = col0 + g * 8;
-                    if (col >= p.N) break;
-                    float o[8];
-#pragma unroll
-                    for (int i = 0; i < 8; i++) o[i] = v[g * 8 + i] * p.alpha;
-                    if (p.bias) {
-                        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
-                        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const float2 f = unpack_bf16x2(bw[i]);
-                            o[2 * i] += f.x;
-                            o[2 * i + 1] += f.y;
-                        }
-                    }
-                    if (p.f32) {
-                        float* dst = p.ws
-                                         ? p.ws + size_t(tc.split) * p.ws_split_stride + size_t(row) * p.N + col
-                                         : reinterpret_cast<float*>(p.C) + size_t(row) * p.ldc + col;
-                        float4 lo = make_float4(o[0], o[1], o[2], o[3]);
-                        float4 hi = make_float4(o[4], o[5], o[6], o[7]);
-                        if (p.accumulate && !p.ws) {
-                            const float4 a = *reinterpret_cast<const float4*>(dst);
-                            const float4 b = *reinterpret_cast<const float4*>(dst + 4);
-                            lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
-                            hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
-                        }
-                        *reinterpret_cast<float4*>(dst) = lo;
-                        *reinterpret_cast<float4*>(dst + 4) = hi;
+                        for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
                     } else {
-                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col;
-                        if (p.residual) {
-                            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldc + col);
-                            const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+                        uint32_t r[16];
+                        tmem_ld_x16(taddr + c * CW, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+                    }
+                    if (!row_ok) continue;
+#pragma unroll
+                    for (int g = 0; g < CW / 8; g++) {
+                        const int col = col0 + g * 8;
+                        if (col >= p.N) break;
+                        float o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) o[i] = v[g * 8 + i] * p.alpha;
+                        if (p.bias) {
+                            const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
                             for (int i = 0; i < 4; i++) {
-                                const float2 f = unpack_bf16x2(rw[i]);
+                                const float2 f = unpack_bf16x2(bw[i]);
                                 o[2 * i] += f.x;
                                 o[2 * i + 1] += f.y;
                             }
                         }
-                        uint4 w;
-                        w.x = pack_bf16x2(o[0], o[1]);
-                        w.y = pack_bf16x2(o[2], o[3]);
-                        w.z = pack_bf16x2(o[4], o[5]);
-                        w.w = pack_bf16x2(o[6], o[7]);
-                        *reinterpret_cast<uint4*>(dst) = w;
+                        if (p.f32) {
+                            float* dst = p.ws
+                                             ? p.ws + size_t(tc.split) * p.ws_split_stride + size_t(row) * p.N + col
+                                             : reinterpret_cast<float*>(p.C) + size_t(row) * p.ldc + col;
+                            float4 lo = make_float4(o[0], o[1], o[2], o[3]);
+                            float4 hi = make_float4(o[4], o[5], o[6], o[7]);
+                            if (p.accumulate && !p.ws) {
+                                const float4 a = *reinterpret_cast<const float4*>(dst);
+                                const float4 b = *reinterpret_cast<const float4*>(dst + 4);
+                                lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+                                hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+                            }
+                            *reinterpret_cast<float4*>(dst) = lo;
+                            *reinterpret_cast<float4*>(dst + 4) = hi;
+                        } else {
+                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col;
+                            if (p.residual) {
+                                const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldc + col);
+                                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    const float2 f = unpack_bf16x2(rw[i]);
+                                    o[2 * i] += f.x;
+                                    o[2 * i + 1] += f.y;
+                                }
+                            }
+                            uint4 w;
+                            w.x = pack_bf16x2(o[0], o[1]);
+                            w.y = pack_bf16x2(o[2], o[3]);
+                            w.z = pack_bf16x2(o[4], o[5]);
+                            w.w = pack_bf16x2(o[6], o[7]);
+                            *reinterpret_cast<uint4*>(dst) = w;
+                        }
                     }
                 }
             }
@@ -313,30 +328,50 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, l
     *dst = accumulate ? *dst + s : s;
 }
 
-template <int BN>
+template <int BN, int MH>
 int launch(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int total_tiles) {
     static bool attr_set[64] = {};
     const int dev = ctx->device & 63;
     if (!attr_set[dev]) {
-        TA_CUDA(ctx, cudaFuncSetAttribute(seg_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          int(Cfg<BN>::SMEM)));
+        TA_CUDA(ctx, cudaFuncSetAttribute(seg_gemm_kernel<BN, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          int(Cfg<BN, MH>::SMEM)));
         attr_set[dev] = true;
     }
     const int grid = std::min(total_tiles, ctx->sm_count);
-    seg_gemm_kernel<BN><<<grid, 192, Cfg<BN>::SMEM, stream>>>(p);
+    seg_gemm_kernel<BN, MH><<<grid, 192, Cfg<BN, MH>::SMEM, stream>>>(p);
     TA_LAUNCH_CHECK(ctx, "seg_gemm_kernel");
     return TA_OK;
+}
+
+struct TileChoice { int bn, mh; };
+
+// Tile shape by a small cost model: waves of tiles over the SMs x (main-loop clocks / delivery
+// efficiency of the shape + non-overlapped per-tile clocks).  The efficiencies are measured ratios of
+// achieved to peak tensor throughput of each shape on large problems.
+TileChoice pick_tile(int M, int N, double ksum, bool any_a_mn, int sms) {
+    if (N <= 16) return {16, 1};
+    if (N <= 32) return {32, 1};
+    if (N <= 64) return {64, 1};
+    struct Cand { int bn, mh; double eff, fixed; };
+    static const Cand cands[] = {{256, 2, 0.84, 2600}, {224, 2, 0.82, 2400}, {256, 1, 0.70, 400},
+                                 {224, 1, 0.68, 400},  {128, 1, 0.52, 300},  {64, 1, 0.30, 250}};
+    TileChoice best{64, 1};
+    double best_t = 1e300;
+    for (const Cand& c : cands) {
+        if (c.mh == 2 && (any_a_mn || M < 256)) continue;
+        const long tiles = long((M + 128 * c.mh - 1) / (128 * c.mh)) * ((N + c.bn - 1) / c.bn);
+        const long waves = (tiles + sms - 1) / sms;
+        const double t = waves * (128.0 * c.mh * c.bn * ksum * 2.0 / 8192.0 / c.eff + c.fixed);
+        if (t < best_t) { best_t = t; best = {c.bn, c.mh}; }
+    }
+    return best;
 }
 
 int pick_bn(int N) {
     if (N <= 16) return 16;
     if (N <= 32) return 32;
     if (N <= 64) return 64;
-    for (int bn : {256, 128}) {
-        const int padded = (N + bn - 1) / bn * bn;
-        if (double(padded - N) / N <= 0.04) return bn;
-    }
-    return 64;
+    return 128;
 }
 
 }  // namespace
@@ -345,12 +380,28 @@ int tokens_gemm_splits(const ta_ctx* ctx, int M, int N, int K) {
     const int bn = pick_bn(N);
     const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     const int nkb = (K + BK - 1) / BK;
-    // enough CTAs to pull the token-major operands through every SM, but at least 8 k-blocks each
-    const int want = std::min({(2 * ctx->sm_count + tiles - 1) / tiles, (nkb + 7) / 8, 256});
-    return std::max(2, want);   // >= 2 selects the partial + fixed-order reduce path (transpose / accumulate)
+    // Split the token dimension so that tiles x splits fills whole waves of SMs (at most ~2 waves, at
+    // least 4 k-blocks per split); >= 2 always, because the partial + fixed-order reduce path also
+    // provides the += and the transposed store.
+    const int sms = ctx->sm_count;
+    const int smax = std::max(2, std::min({nkb / 4, 256, (2 * sms + tiles - 1) / tiles}));
+    int best = 2;
+    double best_u = -1;
+    for (int sp = 2; sp <= smax; sp++) {
+        const long ctas = long(tiles) * sp;
+        const double u = double(ctas) / double((ctas + sms - 1) / sms * sms);
+        if (u > best_u + 1e-9 || (u > best_u - 0.02 && sp > best && ctas <= 2L * sms)) { best_u = std::max(u, best_u); best = sp; }
+    }
+    return best;
 }
 size_t tokens_gemm_ws_bytes(const ta_ctx* ctx, int M, int N, int K) {
     return size_t(tokens_gemm_splits(ctx, M, N, K)) * M * N * sizeof(float);
+}
+size_t tokens_gemm_ws_bytes_max(const ta_ctx* ctx, int M, int N) {
+    const int bn = pick_bn(N);
+    const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const int smax = std::max(2, std::min(256, (2 * ctx->sm_count + tiles - 1) / tiles));
+    return size_t(smax) * M * N * sizeof(float);
 }
 
 int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* segs, int nseg, const GemmOut& out) {
@@ -367,7 +418,11 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
         return fail(ctx, TA_ERR_INVALID, "seg_gemm: transposed output only through the split-K reduce");
     if (out.accumulate && !out.f32) return fail(ctx, TA_ERR_INVALID, "seg_gemm: accumulate needs fp32 output");
 
-    const int bn = pick_bn(N);
+    double ksum_all = 0;
+    bool any_a_mn = false;
+    for (int s = 0; s < nseg; s++) { ksum_all += segs[s].K; any_a_mn = any_a_mn || segs[s].a_mn; }
+    const TileChoice tcfg = out.split_k > 1 ? TileChoice{pick_bn(N), 1} : pick_tile(M, N, ksum_all, any_a_mn, ctx->sm_count);
+    const int bn = tcfg.bn, tile_m = 128 * tcfg.mh;
     SegGemmParams p;
     std::memset(&p, 0, sizeof(p));
     for (int s = 0; s < nseg; s++) {
@@ -379,7 +434,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
             return fail(ctx, TA_ERR_INVALID, "seg_gemm: MN-major A needs M % 8 == 0");
         int rc;
         auto get_tmap_bf16 = out.no_host_state ? encode_tmap_bf16 : ta::get_tmap_bf16;
-        if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, 128, &p.tmA[s]);
+        if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, uint32_t(tile_m), &p.tmA[s]);
         else         rc = get_tmap_bf16(ctx, g.A, uint64_t(M), uint64_t(g.K), uint64_t(g.lda) * 2, 64, 64, &p.tmA[s]);
         if (rc) return rc;
         if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(bn), &p.tmB[s]);
@@ -394,7 +449,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     p.bias = out.bias; p.residual = out.residual; p.status = ctx->d_status;
     p.split_k = 1; p.kb_per_split = 0;
 
-    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + bn - 1) / bn;
+    const int m_tiles = (M + tile_m - 1) / tile_m, n_tiles = (N + bn - 1) / bn;
     if (out.split_k > 1) {
         const int nkb = (segs[0].K + BK - 1) / BK;
         const int splits = std::min(out.split_k, nkb);
@@ -416,12 +471,17 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     for (int s = 0; s < nseg; s++) ksum += segs[s].K;
     ProfScope prof(out.no_host_state ? nullptr : ctx, stream, bn >= 128 ? PROF_GEMM : PROF_GEMM_SKINNY, 2.0 * M * N * ksum);
     int rc;
-    switch (bn) {
-        case 16:  rc = launch<16>(ctx, stream, p, total); break;
-        case 32:  rc = launch<32>(ctx, stream, p, total); break;
-        case 64:  rc = launch<64>(ctx, stream, p, total); break;
-        case 128: rc = launch<128>(ctx, stream, p, total); break;
-        default:  rc = launch<256>(ctx, stream, p, total); break;
+    if (tcfg.mh == 2) {
+        rc = bn == 224 ? launch<224, 2>(ctx, stream, p, total) : launch<256, 2>(ctx, stream, p, total);
+    } else {
+        switch (bn) {
+            case 16:  rc = launch<16, 1>(ctx, stream, p, total); break;
+            case 32:  rc = launch<32, 1>(ctx, stream, p, total); break;
+            case 64:  rc = launch<64, 1>(ctx, stream, p, total); break;
+            case 128: rc = launch<128, 1>(ctx, stream, p, total); break;
+            case 224: rc = launch<224, 1>(ctx, stream, p, total); break;
+            default:  rc = launch<256, 1>(ctx, stream, p, total); break;
+        }
     }
     if (rc) return rc;
     if (out.split_k > 1) {

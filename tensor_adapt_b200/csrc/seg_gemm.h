@@ -48,6 +48,7 @@ struct GemmOut {
 // of partials that many splits need.
 int tokens_gemm_splits(const ta_ctx* ctx, int M, int N, int K);
 size_t tokens_gemm_ws_bytes(const ta_ctx* ctx, int M, int N, int K);
+size_t tokens_gemm_ws_bytes_max(const ta_ctx* ctx, int M, int N);   // for any token count
 
 // Launches on `stream`; asynchronous. Returns TA_OK or a negative error code.
 int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* segs, int nseg, const GemmOut& out);

@@ -306,8 +306,7 @@ int ta_trainer_create(ta_ctx* ctx, const ta_model_config* mc, const ta_adapter_c
                 target_dims(c, tg, &sl.in, &sl.out);
                 sl.offA = off; off += (long(r) * sl.in + 127) / 128 * 128;
                 sl.offB = off; off += (long(sl.out) * r + 127) / 128 * 128;
-                sk_need = std::max({sk_need, tokens_gemm_ws_bytes(ctx, sl.out, r, int(BT)),
-                                    tokens_gemm_ws_bytes(ctx, sl.in, r, int(BT))});
+                sk_need = std::max({sk_need, tokens_gemm_ws_bytes_max(ctx, sl.out, r), tokens_gemm_ws_bytes_max(ctx, sl.in, r)});
             }
         t->lora_n = off;
         t->master = static_cast<float*>(Lo.take(size_t(off) * 4));
