@@ -15,7 +15,6 @@
 // work with one thread per tile row (TMEM lane).  Every wait is bounded.
 #include <algorithm>
 #include <cmath>
-#include <cstdlib>
 
 #include "ctx.h"
 #include "ptx.cuh"
@@ -53,29 +52,36 @@ struct Tile {
     static constexpr uint32_t BYTES64 = NC * 8192u;    // [64 rows][HD]
 };
 
+// The MMA-issuing thread is a serial resource: 16-24 MMAs per tile iteration.  Descriptors are therefore
+// built once per buffer and advanced with a single 64-bit add per MMA (the start-address field counts
+// 16-byte units; shared-memory addresses stay below 256 KB, so the add never carries out of the field).
+__device__ __forceinline__ uint64_t desc_k(uint32_t saddr) { return smem_desc_sw128(saddr, 16, 1024); }
+__device__ __forceinline__ uint64_t desc_mn(uint32_t saddr, uint32_t chunk_bytes) {
+    return smem_desc_sw128(saddr, chunk_bytes, 1024);
+}
+
 // D[128, N] (+)= A[128, HD] . B[N, HD]^T, both K-major, NC chunks of a_chunk / b_chunk bytes
 template <int HD, int N>
-__device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_smem, uint32_t a_chunk, uint32_t b_smem,
+__device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint64_t a_desc, uint32_t a_chunk, uint64_t b_desc,
                                        uint32_t b_chunk, bool accumulate) {
     constexpr uint32_t idesc = umma_idesc_bf16(128, N, false, false);
 #pragma unroll
     for (int c = 0; c < Tile<HD>::NC; c++)
 #pragma unroll
         for (int ki = 0; ki < 4; ki++)
-            umma_bf16(d_tmem, smem_desc_sw128(a_smem + c * a_chunk + ki * 32, 16, 1024),
-                      smem_desc_sw128(b_smem + c * b_chunk + ki * 32, 16, 1024), idesc, (accumulate || c || ki) ? 1u : 0u);
+            umma_bf16(d_tmem, a_desc + ((c * a_chunk + ki * 32) >> 4), b_desc + ((c * b_chunk + ki * 32) >> 4), idesc,
+                      (accumulate || c || ki) ? 1u : 0u);
 }
 
 // D[128, HD] (+)= A[128, KT] . B[KT (k), HD (n)]: A K-major (64-column chunks 16384 B apart), B a
-// [KT rows][HD] tile read MN-major (n chunks b_chunk bytes apart, 8-row groups 1024 B apart)
+// [KT rows][HD] tile read MN-major (b_desc made by desc_mn with the n-chunk stride; 16 k-rows = 2048 B)
 template <int HD, int KT>
-__device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, uint32_t b_chunk,
-                                        bool accumulate) {
+__device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, bool accumulate) {
     constexpr uint32_t idesc = umma_idesc_bf16(128, HD, false, true);
 #pragma unroll
     for (int ks = 0; ks < KT / 16; ks++)
-        umma_bf16(d_tmem, smem_desc_sw128(a_smem + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                  smem_desc_sw128(b_smem + ks * 2048, b_chunk, 1024), idesc, (accumulate || ks) ? 1u : 0u);
+        umma_bf16(d_tmem, a_desc + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), b_desc + ((ks * 2048) >> 4), idesc,
+                  (accumulate || ks) ? 1u : 0u);
 }
 
 template <int HD>
@@ -91,6 +97,8 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, uint32_t chunk_bytes, co
 // A running maximum is only raised when the new one exceeds it by more than this (log2 units): the
 // probabilities then stay below 2^8 and the accumulator in TMEM rarely needs rescaling.
 constexpr float kRescaleThreshold = 8.f;
+constexpr int kDqStages = 4;    // K/V ring of the dQ kernel (64-row tiles)
+constexpr int kDkvStages = 4;   // Q/dO ring of the dK/dV kernel (64-row tiles)
 
 // ─────────────────────────────── forward ───────────────────────────────
 // TMEM: S buffers at columns [0,128) and [128,256), O accumulator at [256, 256+HD).
@@ -98,13 +106,14 @@ constexpr float kRescaleThreshold = 8.f;
 template <int HD>
 __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     constexpr uint32_t TB = Tile<HD>::BYTES;
-    constexpr uint32_t OFF_Q = 0, OFF_K = TB, OFF_V = 3 * TB, OFF_P = 5 * TB, OFF_BAR = 5 * TB + 32768;
+    constexpr int KS = 3;   // K ring: scores run two tiles ahead of the softmax, so three K tiles are live
+    constexpr uint32_t OFF_Q = 0, OFF_K = TB, OFF_V = (1 + KS) * TB, OFF_P = (3 + KS) * TB, OFF_BAR = (3 + KS) * TB + 32768;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
-             *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 14;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 4, *v_full = bars + 7, *v_empty = bars + 9,
+             *s_full = bars + 11, *s_empty = bars + 13, *p_full = bars + 15, *o_full = bars + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -119,8 +128,8 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        for (int i = 0; i < KS; i++) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
-            mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
         }
@@ -140,11 +149,11 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
             mbar_arrive_expect_tx(q_full, TB);
             load_tile<HD>(smem + OFF_Q, 16384, &p.tmQ, q_full, h * HD, b * p.T + q0);
             for (int j = 0; j < n; j++) {
-                const int st = j & 1;
+                const int st = j & 1, kst = j % KS;
                 const uint32_t ph = (j >> 1) & 1;
-                ATT_WAIT(&k_empty[st], ph ^ 1u, DS_TIMEOUT_PRODUCER);
-                mbar_arrive_expect_tx(&k_full[st], TB);
-                load_tile<HD>(smem + OFF_K + st * TB, 16384, &p.tmK, &k_full[st], hk * HD, b * p.T + j * 128);
+                ATT_WAIT(&k_empty[kst], ((j / KS) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
+                mbar_arrive_expect_tx(&k_full[kst], TB);
+                load_tile<HD>(smem + OFF_K + kst * TB, 16384, &p.tmK, &k_full[kst], hk * HD, b * p.T + j * 128);
                 ATT_WAIT(&v_empty[st], ph ^ 1u, DS_TIMEOUT_PRODUCER);
                 mbar_arrive_expect_tx(&v_full[st], TB);
                 load_tile<HD>(smem + OFF_V + st * TB, 16384, &p.tmV, &v_full[st], hk * HD, b * p.T + j * 128);
@@ -152,18 +161,19 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t sQ = smem_u32(smem + OFF_Q), sK = smem_u32(smem + OFF_K), sV = smem_u32(smem + OFF_V),
-                           sP = smem_u32(smem + OFF_P);
+            const uint64_t dQd = desc_k(smem_u32(smem + OFF_Q)), dKd = desc_k(smem_u32(smem + OFF_K)),
+                           dVd = desc_mn(smem_u32(smem + OFF_V), 16384), dPd = desc_k(smem_u32(smem + OFF_P));
             ATT_WAIT(q_full, 0, DS_TIMEOUT_MMA);
-            for (int j = -1; j < n; j++) {
-                if (j + 1 < n) {   // scores of the next key tile, into the other S buffer
-                    const int jn = j + 1, st = jn & 1;
-                    const uint32_t ph = (jn >> 1) & 1;
-                    ATT_WAIT(&k_full[st], ph, DS_TIMEOUT_MMA);
-                    ATT_WAIT(&s_empty[st], ph ^ 1u, DS_TIMEOUT_MMA);
+            // Scores run TWO tiles ahead of the softmax: S(j+2) is issued as soon as the softmax warps have
+            // pulled S(j) into registers, so a finished softmax never waits for its next tile.
+            for (int j = -2; j < n; j++) {
+                if (j + 2 < n) {
+                    const int jn = j + 2, st = jn & 1, kst = jn % KS;
+                    ATT_WAIT(&k_full[kst], (jn / KS) & 1, DS_TIMEOUT_MMA);
+                    ATT_WAIT(&s_empty[st], ((jn >> 1) & 1) ^ 1u, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kk<HD, 128>(tmem + st * 128, sQ, 16384, sK + st * TB, 16384, false);
-                    umma_commit(&k_empty[st]);
+                    mma_kk<HD, 128>(tmem + st * 128, dQd, 16384, dKd + ((kst * TB) >> 4), 16384, false);
+                    umma_commit(&k_empty[kst]);
                     umma_commit(&s_full[st]);
                 }
                 if (j >= 0) {      // O += P_j . V_j once the softmax warps have published P_j (and rescaled O)
@@ -171,7 +181,7 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
                     ATT_WAIT(&v_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
                     ATT_WAIT(p_full, j & 1, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kmn<HD, 128>(TM_O, sP, sV + st * TB, 16384, j > 0);
+                    mma_kmn<HD, 128>(TM_O, dPd, dVd + ((st * TB) >> 4), j > 0);
                     umma_commit(&v_empty[st]);
                     umma_commit(o_full);
                 }
@@ -217,14 +227,23 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
                 m = mx;
                 rescale = true;
             }
+            // Three separate passes so that the 128 special-function ops are issued back to back: with one
+            // softmax warp per scheduler there is no other warp to hide the MUFU latency behind.
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) s[c][i] = __float_as_uint(__uint_as_float(s[c][i]) - m);
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) s[c][i] = __float_as_uint(ex2_approx(__uint_as_float(s[c][i])));
             uint32_t pk[64];
             float sum = 0.f;
 #pragma unroll
             for (int c = 0; c < 4; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2_approx(__uint_as_float(s[c][i]) - m);
-                    const float p1 = ex2_approx(__uint_as_float(s[c][i + 1]) - m);
+                    const float p0 = __uint_as_float(s[c][i]), p1 = __uint_as_float(s[c][i + 1]);
                     sum += p0 + p1;
                     pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
                 }
@@ -320,14 +339,16 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __
 template <int HD>
 __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
     constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
-    constexpr uint32_t OFF_Q = 0, OFF_DO = TB, OFF_K = 2 * TB, OFF_V = 2 * TB + 2 * TB64, OFF_DS = 2 * TB + 4 * TB64,
-                       OFF_BAR = OFF_DS + 32768;
+    constexpr int KVST = kDqStages;   // K/V ring depth: a stage is only released after dQ += dS.K, so the
+                                      // prefetch distance must cover the TMA latency
+    constexpr uint32_t OFF_Q = 0, OFF_DO = TB, OFF_K = 2 * TB, OFF_V = 2 * TB + KVST * TB64,
+                       OFF_DS = 2 * TB + 2 * KVST * TB64, OFF_BAR = OFF_DS + 32768;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-    uint64_t *qdo_full = bars, *kv_full = bars + 1, *kv_empty = bars + 3, *s_full = bars + 5, *s_empty = bars + 7,
-             *ds_full = bars + 9, *ds_empty = bars + 11, *dq_full = bars + 13;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t *qdo_full = bars, *kv_full = bars + 1, *kv_empty = bars + 1 + KVST, *s_full = bars + 1 + 2 * KVST,
+             *s_empty = s_full + 2, *ds_full = s_full + 4, *ds_empty = s_full + 6, *dq_full = s_full + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -340,8 +361,8 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
 
     if (threadIdx.x == 0) {
         mbar_init(qdo_full, 1);
+        for (int i = 0; i < KVST; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
-            mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
             mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
             mbar_init(&ds_full[i], 4); mbar_init(&ds_empty[i], 1);
         }
@@ -362,8 +383,8 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
             load_tile<HD>(smem + OFF_Q, 16384, &p.tmQ, qdo_full, h * HD, b * p.T + q0);
             load_tile<HD>(smem + OFF_DO, 16384, &p.tmdO, qdo_full, h * HD, b * p.T + q0);
             for (int j = 0; j < n; j++) {
-                const int st = j & 1;
-                ATT_WAIT(&kv_empty[st], ((j >> 1) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
+                const int st = j % KVST;
+                ATT_WAIT(&kv_empty[st], ((j / KVST) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
                 mbar_arrive_expect_tx(&kv_full[st], 2 * TB64);
                 load_tile<HD>(smem + OFF_K + st * TB64, 8192, &p.tmK64, &kv_full[st], hk * HD, b * p.T + j * 64);
                 load_tile<HD>(smem + OFF_V + st * TB64, 8192, &p.tmV64, &kv_full[st], hk * HD, b * p.T + j * 64);
@@ -371,26 +392,26 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t sQ = smem_u32(smem + OFF_Q), sDO = smem_u32(smem + OFF_DO), sK = smem_u32(smem + OFF_K),
-                           sV = smem_u32(smem + OFF_V), sDS = smem_u32(smem + OFF_DS);
+            const uint64_t dQd = desc_k(smem_u32(smem + OFF_Q)), dDOd = desc_k(smem_u32(smem + OFF_DO)),
+                           dKk = desc_k(smem_u32(smem + OFF_K)), dVk = desc_k(smem_u32(smem + OFF_V)),
+                           dKmn = desc_mn(smem_u32(smem + OFF_K), 8192), dDSd = desc_k(smem_u32(smem + OFF_DS));
             ATT_WAIT(qdo_full, 0, DS_TIMEOUT_MMA);
-            for (int j = -1; j < n; j++) {
-                if (j + 1 < n) {
-                    const int jn = j + 1, st = jn & 1;
-                    const uint32_t ph = (jn >> 1) & 1;
-                    ATT_WAIT(&kv_full[st], ph, DS_TIMEOUT_MMA);
-                    ATT_WAIT(&s_empty[st], ph ^ 1u, DS_TIMEOUT_MMA);
+            for (int j = -2; j < n; j++) {   // S / dP run two sub-tiles ahead of the element-wise warps
+                if (j + 2 < n) {
+                    const int jn = j + 2, st = jn & 1, ks = jn % KVST;
+                    ATT_WAIT(&kv_full[ks], (jn / KVST) & 1, DS_TIMEOUT_MMA);
+                    ATT_WAIT(&s_empty[st], ((jn >> 1) & 1) ^ 1u, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kk<HD, 64>(TM_S + st * 64, sQ, 16384, sK + st * TB64, 8192, false);
-                    mma_kk<HD, 64>(TM_DP + st * 64, sDO, 16384, sV + st * TB64, 8192, false);
+                    mma_kk<HD, 64>(TM_S + st * 64, dQd, 16384, dKk + ((ks * TB64) >> 4), 8192, false);
+                    mma_kk<HD, 64>(TM_DP + st * 64, dDOd, 16384, dVk + ((ks * TB64) >> 4), 8192, false);
                     umma_commit(&s_full[st]);
                 }
                 if (j >= 0) {
-                    const int st = j & 1;
+                    const int st = j & 1, ks = j % KVST;
                     ATT_WAIT(&ds_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kmn<HD, 64>(TM_DQ, sDS + st * 16384, sK + st * TB64, 8192, j > 0);
-                    umma_commit(&kv_empty[st]);
+                    mma_kmn<HD, 64>(TM_DQ, dDSd + ((st * 16384) >> 4), dKmn + ((ks * TB64) >> 4), j > 0);
+                    umma_commit(&kv_empty[ks]);
                     umma_commit(&ds_empty[st]);
                 }
             }
@@ -421,20 +442,27 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[st]);
             const bool diag = (j * 64 + 63 > q0);
+            // staged so that the 64 special-function ops issue back to back (see the forward kernel)
+#pragma unroll
+            for (int c = 0; c < 2; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float a = __uint_as_float(rs[c][i]) * p.scale_log2 - lse2;
+                    if (diag && (j * 64 + c * 32 + i > q_idx)) a = -INFINITY;
+                    rs[c][i] = __float_as_uint(a);
+                }
+#pragma unroll
+            for (int c = 0; c < 2; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) rs[c][i] = __float_as_uint(ex2_approx(__uint_as_float(rs[c][i])));
             uint32_t pk[32];
 #pragma unroll
             for (int c = 0; c < 2; c++)
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = ex2_approx(__uint_as_float(rs[c][i]) * p.scale_log2 - lse2);
-                    float p1 = ex2_approx(__uint_as_float(rs[c][i + 1]) * p.scale_log2 - lse2);
-                    if (diag) {
-                        if (j * 64 + c * 32 + i > q_idx) p0 = 0.f;
-                        if (j * 64 + c * 32 + i + 1 > q_idx) p1 = 0.f;
-                    }
-                    pk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * (__uint_as_float(rp[c][i]) - dlt) * p.scale,
-                                                        p1 * (__uint_as_float(rp[c][i + 1]) - dlt) * p.scale);
-                }
+                for (int i = 0; i < 32; i += 2)
+                    pk[c * 16 + (i >> 1)] =
+                        pack_bf16x2(__uint_as_float(rs[c][i]) * (__uint_as_float(rp[c][i]) - dlt) * p.scale,
+                                    __uint_as_float(rs[c][i + 1]) * (__uint_as_float(rp[c][i + 1]) - dlt) * p.scale);
             ATT_WAIT(&ds_empty[st], ph ^ 1u, DS_TIMEOUT_SOFTMAX);
             uint8_t* sDS = smem + OFF_DS + st * 16384;
 #pragma unroll
@@ -481,14 +509,15 @@ done:
 template <int HD>
 __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
     constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
-    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + 2 * TB64, OFF_PT = 2 * TB + 4 * TB64,
-                       OFF_DST = OFF_PT + 32768, OFF_STAT = OFF_DST + 32768, OFF_BAR = OFF_STAT + 1024;
+    constexpr int QST = kDkvStages;   // Q/dO ring depth (a stage is released only after dV, dK consumed it)
+    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + QST * TB64, OFF_PT = 2 * TB + 2 * QST * TB64,
+                       OFF_DST = OFF_PT + 16384, OFF_STAT = OFF_DST + 16384, OFF_BAR = OFF_STAT + 1024;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-    uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 3, *s_full = bars + 5, *s_empty = bars + 7,
-             *p_full = bars + 9, *p_empty = bars + 11, *acc_full = bars + 13, *stat_full = bars + 14;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 1 + QST, *s_full = bars + 1 + 2 * QST,
+             *s_empty = s_full + 2, *p_full = s_full + 4, *p_empty = s_full + 6, *acc_full = s_full + 8, *stat_full = s_full + 9;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* stat = reinterpret_cast<float*>(smem + OFF_STAT);   // [2 buffers][lse2 64 | delta 64]
 
@@ -504,11 +533,11 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1); mbar_init(acc_full, 1); mbar_init(stat_full, 128);
+        for (int i = 0; i < QST; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
-            mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1);
             mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
-            mbar_init(&p_full[i], 4); mbar_init(&p_empty[i], 1);
         }
+        mbar_init(p_full, 4); mbar_init(p_empty, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -525,8 +554,8 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
             load_tile<HD>(smem + OFF_K, 16384, &p.tmK, kv_full, hk * HD, b * p.T + kv0);
             load_tile<HD>(smem + OFF_V, 16384, &p.tmV, kv_full, hk * HD, b * p.T + kv0);
             for (int it = 0; it < iters; it++) {
-                const int h = hk * G + it / per_head, qs = 2 * kt + it % per_head, st = it & 1;
-                ATT_WAIT(&qdo_empty[st], ((it >> 1) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
+                const int h = hk * G + it / per_head, qs = 2 * kt + it % per_head, st = it % QST;
+                ATT_WAIT(&qdo_empty[st], ((it / QST) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
                 mbar_arrive_expect_tx(&qdo_full[st], 2 * TB64);
                 load_tile<HD>(smem + OFF_Q + st * TB64, 8192, &p.tmQ64, &qdo_full[st], h * HD, b * p.T + qs * 64);
                 load_tile<HD>(smem + OFF_DO + st * TB64, 8192, &p.tmdO64, &qdo_full[st], h * HD, b * p.T + qs * 64);
@@ -534,28 +563,29 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t sK = smem_u32(smem + OFF_K), sV = smem_u32(smem + OFF_V), sQ = smem_u32(smem + OFF_Q),
-                           sDO = smem_u32(smem + OFF_DO), sPT = smem_u32(smem + OFF_PT), sDST = smem_u32(smem + OFF_DST);
+            const uint64_t dKd = desc_k(smem_u32(smem + OFF_K)), dVd = desc_k(smem_u32(smem + OFF_V)),
+                           dQk = desc_k(smem_u32(smem + OFF_Q)), dDOk = desc_k(smem_u32(smem + OFF_DO)),
+                           dQmn = desc_mn(smem_u32(smem + OFF_Q), 8192), dDOmn = desc_mn(smem_u32(smem + OFF_DO), 8192),
+                           dPTd = desc_k(smem_u32(smem + OFF_PT)), dDSTd = desc_k(smem_u32(smem + OFF_DST));
             ATT_WAIT(kv_full, 0, DS_TIMEOUT_MMA);
-            for (int it = -1; it < iters; it++) {
-                if (it + 1 < iters) {
-                    const int in = it + 1, st = in & 1;
-                    const uint32_t ph = (in >> 1) & 1;
-                    ATT_WAIT(&qdo_full[st], ph, DS_TIMEOUT_MMA);
-                    ATT_WAIT(&s_empty[st], ph ^ 1u, DS_TIMEOUT_MMA);
+            for (int it = -2; it < iters; it++) {   // S^T / dP^T run two sub-tiles ahead
+                if (it + 2 < iters) {
+                    const int in = it + 2, st = in & 1, qs_ = in % QST;
+                    ATT_WAIT(&qdo_full[qs_], (in / QST) & 1, DS_TIMEOUT_MMA);
+                    ATT_WAIT(&s_empty[st], ((in >> 1) & 1) ^ 1u, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kk<HD, 64>(TM_ST + st * 64, sK, 16384, sQ + st * TB64, 8192, false);     // S^T  = K . Q^T
-                    mma_kk<HD, 64>(TM_DPT + st * 64, sV, 16384, sDO + st * TB64, 8192, false);   // dP^T = V . dO^T
+                    mma_kk<HD, 64>(TM_ST + st * 64, dKd, 16384, dQk + ((qs_ * TB64) >> 4), 8192, false);     // S^T  = K . Q^T
+                    mma_kk<HD, 64>(TM_DPT + st * 64, dVd, 16384, dDOk + ((qs_ * TB64) >> 4), 8192, false);   // dP^T = V . dO^T
                     umma_commit(&s_full[st]);
                 }
                 if (it >= 0) {
-                    const int st = it & 1;
-                    ATT_WAIT(&p_full[st], (it >> 1) & 1, DS_TIMEOUT_MMA);
+                    const int qs_ = it % QST;
+                    ATT_WAIT(p_full, it & 1, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kmn<HD, 64>(TM_DV, sPT + st * 16384, sDO + st * TB64, 8192, it > 0);    // dV += P^T . dO
-                    mma_kmn<HD, 64>(TM_DK, sDST + st * 16384, sQ + st * TB64, 8192, it > 0);    // dK += dS^T . Q
-                    umma_commit(&qdo_empty[st]);
-                    umma_commit(&p_empty[st]);
+                    mma_kmn<HD, 64>(TM_DV, dPTd, dDOmn + ((qs_ * TB64) >> 4), it > 0);    // dV += P^T . dO
+                    mma_kmn<HD, 64>(TM_DK, dDSTd, dQmn + ((qs_ * TB64) >> 4), it > 0);    // dK += dS^T . Q
+                    umma_commit(&qdo_empty[qs_]);
+                    umma_commit(p_empty);
                 }
             }
             umma_commit(acc_full);
@@ -602,25 +632,33 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[st]);
             const bool diag = (qs * 64 < kv0 + 127);
+#pragma unroll
+            for (int c = 0; c < 2; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const int col = c * 32 + i;
+                    float a = __uint_as_float(rs[c][i]) * p.scale_log2 - lse2[col];
+                    if (diag && (kv_idx > qs * 64 + col)) a = -INFINITY;
+                    rs[c][i] = __float_as_uint(a);
+                }
+#pragma unroll
+            for (int c = 0; c < 2; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) rs[c][i] = __float_as_uint(ex2_approx(__uint_as_float(rs[c][i])));
             uint32_t pk[32], dk[32];
 #pragma unroll
             for (int c = 0; c < 2; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const int col = c * 32 + i;
-                    float p0 = ex2_approx(__uint_as_float(rs[c][i]) * p.scale_log2 - lse2[col]);
-                    float p1 = ex2_approx(__uint_as_float(rs[c][i + 1]) * p.scale_log2 - lse2[col + 1]);
-                    if (diag) {
-                        if (kv_idx > qs * 64 + col) p0 = 0.f;
-                        if (kv_idx > qs * 64 + col + 1) p1 = 0.f;
-                    }
+                    const float p0 = __uint_as_float(rs[c][i]), p1 = __uint_as_float(rs[c][i + 1]);
                     pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
                     dk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * (__uint_as_float(rp[c][i]) - dlt[col]) * p.scale,
                                                         p1 * (__uint_as_float(rp[c][i + 1]) - dlt[col + 1]) * p.scale);
                 }
-            ATT_WAIT(&p_empty[st], ph ^ 1u, DS_TIMEOUT_SOFTMAX);
-            uint8_t* sPT = smem + OFF_PT + st * 16384;
-            uint8_t* sDST = smem + OFF_DST + st * 16384;
+            ATT_WAIT(p_empty, (it & 1) ^ 1u, DS_TIMEOUT_SOFTMAX);   // dV/dK of the previous sub-tile have read P^T, dS^T
+            uint8_t* sPT = smem + OFF_PT;
+            uint8_t* sDST = smem + OFF_DST;
 #pragma unroll
             for (int g = 0; g < 8; g++) {
                 const uint32_t off = kmajor_off(row, g * 8);
@@ -630,7 +668,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[st]);
+            if (lane == 0) mbar_arrive(p_full);
         }
         ATT_WAIT(acc_full, 0, DS_TIMEOUT_SOFTMAX);
         tcgen05_fence_after_sync();
@@ -666,9 +704,9 @@ done:
     if (warp == 1) { tcgen05_fence_after_sync(); tmem_dealloc(tmem, 512); }
 }
 
-template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 32768 + 256 + 1024; }
-template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 4 * Tile<HD>::BYTES64 + 32768 + 256 + 1024; }
-template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 4 * Tile<HD>::BYTES64 + 65536 + 1024 + 256 + 1024; }
+template <int HD> constexpr size_t fwd_smem() { return 6 * Tile<HD>::BYTES + 32768 + 256 + 1024; }
+template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 2 * kDqStages * Tile<HD>::BYTES64 + 32768 + 256 + 1024; }
+template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 32768 + 1024 + 256 + 1024; }
 
 int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const void* V, const void* dO, int B, int T,
               int Hq, int Hkv, int hd) {
@@ -745,7 +783,6 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
         delta = static_cast<float*>(ws);
     }
     const long warps = long(B) * T * Hq;
-    if (!(delta_scratch && getenv("TA_DEBUG_KEEP_DELTA")))
     attn_delta_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(out), delta, B, T, Hq, head_dim);
     TA_LAUNCH_CHECK(ctx, "attn_delta_kernel");

@@ -10,6 +10,8 @@
 #include "seg_gemm.h"
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "ptx.cuh"
@@ -355,6 +357,12 @@ TileChoice pick_tile(int M, int N, double ksum, bool any_a_mn, int sms) {
     struct Cand { int bn, mh; double eff, fixed; };
     static const Cand cands[] = {{256, 2, 0.84, 2600}, {224, 2, 0.82, 2400}, {256, 1, 0.70, 400},
                                  {224, 1, 0.68, 400},  {128, 1, 0.52, 300},  {64, 1, 0.30, 250}};
+    if (const char* f = std::getenv("TA_GEMM_TILE")) {   // tuning knob: "BN,MH" forces one tile shape
+        int bn = 0, mh = 0;
+        if (std::sscanf(f, "%d,%d", &bn, &mh) == 2 && (mh == 1 || (mh == 2 && !any_a_mn && M >= 256)) &&
+            (bn == 64 || bn == 128 || bn == 224 || bn == 256) && (mh == 1 || bn >= 224))
+            return {bn, mh};
+    }
     TileChoice best{64, 1};
     double best_t = 1e300;
     for (const Cand& c : cands) {
