@@ -305,30 +305,34 @@ done:
     if (warp == 1) { tcgen05_fence_after_sync(); tmem_dealloc(tmem, 512); }
 }
 
-// delta[b,h,t] = sum_d dO[bt, h*hd+d] * O[bt, h*hd+d]; one warp per (token, head)
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                                  float* __restrict__ delta, int B, int T, int Hq, int hd) {
-    const long wid = (blockIdx.x * long(blockDim.x) + threadIdx.x) >> 5;
+// delta[b,h,t] = sum_d dO[bt, h*hd+d] * O[bt, h*hd+d].  One warp per token walks the whole row with
+// 16-byte loads; a head is hd/8 consecutive vectors, i.e. a group of 16 (hd=128) or 8 (hd=64) lanes.
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ dO,
+                                                         const __nv_bfloat16* __restrict__ O, float* __restrict__ delta,
+                                                         int B, int T, int Hq, int hd) {
     const int lane = threadIdx.x & 31;
-    if (wid >= long(B) * T * Hq) return;
-    const int h = int(wid % Hq);
-    const long bt = wid / Hq;
-    const uint4* a = reinterpret_cast<const uint4*>(dO + (bt * Hq + h) * hd);
-    const uint4* o = reinterpret_cast<const uint4*>(O + (bt * Hq + h) * hd);
-    float s = 0.f;
-    if (lane < hd / 8) {
-        const uint4 x = a[lane], y = o[lane];
-        const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float2 f = unpack_bf16x2(xw[i]), g = unpack_bf16x2(yw[i]);
-            s += f.x * g.x + f.y * g.y;
-        }
-    }
-    s = warp_sum(s);
-    if (lane == 0) {
+    const int wpb = blockDim.x >> 5;
+    const int vph = hd / 8;                 // vectors per head (8 or 16)
+    const int nvec = Hq * vph;
+    for (long bt = blockIdx.x * long(wpb) + (threadIdx.x >> 5); bt < long(B) * T; bt += long(gridDim.x) * wpb) {
+        const uint4* a = reinterpret_cast<const uint4*>(dO + bt * Hq * hd);
+        const uint4* o = reinterpret_cast<const uint4*>(O + bt * Hq * hd);
         const int b = int(bt / T), t = int(bt % T);
-        delta[(size_t(b) * Hq + h) * T + t] = s;
+        for (int i0 = 0; i0 < nvec; i0 += 32) {
+            const int i = i0 + lane;
+            float s = 0.f;
+            if (i < nvec) {
+                const uint4 x = a[i], y = o[i];
+                const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float2 f = unpack_bf16x2(xw[k]), g = unpack_bf16x2(yw[k]);
+                    s += f.x * g.x + f.y * g.y;
+                }
+            }
+            for (int off = vph >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+            if (i < nvec && (lane % vph) == 0) delta[(size_t(b) * Hq + i / vph) * T + t] = s;
+        }
     }
 }
 
@@ -782,8 +786,7 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
         if (int rc = get_workspace(ctx, size_t(B) * Hq * T * sizeof(float), &ws)) return rc;
         delta = static_cast<float*>(ws);
     }
-    const long warps = long(B) * T * Hq;
-    attn_delta_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, s>>>(
+    attn_delta_kernel<<<unsigned(std::min<long>((long(B) * T + 7) / 8, long(ctx->sm_count) * 16)), 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(out), delta, B, T, Hq, head_dim);
     TA_LAUNCH_CHECK(ctx, "attn_delta_kernel");
 

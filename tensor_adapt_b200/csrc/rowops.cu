@@ -1,6 +1,7 @@
 // HBM-bound kernels of the training step: RMSNorm, RoPE, SwiGLU, embedding gather, residual / bias
 // adds, casts and cross-entropy.  All use 16-byte vector accesses, FP32 arithmetic inside, and
 // warp-shuffle reductions; none allocates memory.
+#include <algorithm>
 #include <cfloat>
 
 #include "ctx.h"
@@ -148,6 +149,113 @@ __global__ void __launch_bounds__(NT) rms_norm_bwd_kernel(const __nv_bfloat16* _
                 if (arow) {
                     // fused residual-gradient add: out = bf16(add_to + bf16(dx)), the two roundings of
                     // rms_norm_bwd followed by add_inplace
+                    float fa[8];
+                    const uint4 av = arow[i];
+                    unpack8(av, fa);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) o[e] = fa[e] + __bfloat162float(__float2bfloat16(o[e]));
+                }
+                orow[i] = pack8(o);
+            }
+        }
+    }
+}
+
+// Warp-per-row variants: no block-level barrier, 8 independent rows in flight per CTA and several CTAs
+// per SM, which is what keeps enough bytes in flight to approach the HBM rate.  Used when a lane can hold
+// its share of the row (NV 16-byte vectors per lane, D <= 32*NV*8).
+template <int NV>
+__global__ void __launch_bounds__(256) rms_norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ w,
+                                                                __nv_bfloat16* __restrict__ out,
+                                                                float* __restrict__ rms_out, int rows, int D, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int nvec = D / 8;
+    const int wpb = blockDim.x >> 5;
+    const uint4* wv = reinterpret_cast<const uint4*>(w);
+    for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(row) * D);
+        uint4 xv[NV];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = lane + j * 32;
+            if (i < nvec) xv[j] = xr[i];
+        }
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = lane + j * 32;
+            if (i < nvec) {
+                float f[8];
+                unpack8(xv[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; e++) ss += f[e] * f[e];
+            }
+        }
+        ss = warp_sum(ss);
+        const float rms = 1.0f / sqrtf(ss / float(D) + eps);
+        if (lane == 0 && rms_out) rms_out[row] = rms;
+        uint4* orow = reinterpret_cast<uint4*>(out + size_t(row) * D);
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = lane + j * 32;
+            if (i < nvec) {
+                float f[8], g[8];
+                unpack8(xv[j], f);
+                unpack8(__ldg(wv + i), g);
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[e] = f[e] * rms * g[e];
+                orow[i] = pack8(f);
+            }
+        }
+    }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) rms_norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ w,
+                                                                const float* __restrict__ rms_saved,
+                                                                __nv_bfloat16* __restrict__ dx,
+                                                                const __nv_bfloat16* __restrict__ add_to, int rows, int D) {
+    const int lane = threadIdx.x & 31;
+    const int nvec = D / 8;
+    const int wpb = blockDim.x >> 5;
+    const uint4* wv = reinterpret_cast<const uint4*>(w);
+    for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(row) * D);
+        const uint4* dr = reinterpret_cast<const uint4*>(dy + size_t(row) * D);
+        const float rms = rms_saved[row];
+        uint4 xv[NV], dv[NV];
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = lane + j * 32;
+            if (i < nvec) { xv[j] = xr[i]; dv[j] = dr[i]; }
+        }
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = lane + j * 32;
+            if (i < nvec) {
+                float fx[8], fd[8], fw[8];
+                unpack8(xv[j], fx); unpack8(dv[j], fd); unpack8(__ldg(wv + i), fw);
+#pragma unroll
+                for (int e = 0; e < 8; e++) dot += fd[e] * fw[e] * (fx[e] * rms);
+            }
+        }
+        dot = warp_sum(dot);
+        const float corr = dot / float(D);
+        uint4* orow = reinterpret_cast<uint4*>(dx + size_t(row) * D);
+        const uint4* arow = add_to ? reinterpret_cast<const uint4*>(add_to + size_t(row) * D) : nullptr;
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = lane + j * 32;
+            if (i < nvec) {
+                float fx[8], fd[8], fw[8], o[8];
+                unpack8(xv[j], fx); unpack8(dv[j], fd); unpack8(__ldg(wv + i), fw);
+#pragma unroll
+                for (int e = 0; e < 8; e++) o[e] = rms * (fw[e] * fd[e] - (fx[e] * rms) * corr);
+                if (arow) {
                     float fa[8];
                     const uint4 av = arow[i];
                     unpack8(av, fa);
@@ -407,7 +515,12 @@ int ta_rms_norm_fwd(ta_ctx* ctx, const void* x, const void* w, void* out, float*
     auto X = static_cast<const __nv_bfloat16*>(x);
     auto W = static_cast<const __nv_bfloat16*>(w);
     auto O = static_cast<__nv_bfloat16*>(out);
-    if (D / 8 <= 128 * kMaxVec) rms_norm_fwd_kernel<128><<<grid, 128, 0, s>>>(X, W, O, rms_out, rows, D, eps);
+    const int nv = (D / 8 + 31) / 32;
+    const unsigned wgrid = unsigned(std::min<long>((rows + 7) / 8, long(ctx->sm_count) * 8));
+    if (nv <= 4)       rms_norm_fwd_warp_kernel<4><<<wgrid, 256, 0, s>>>(X, W, O, rms_out, rows, D, eps);
+    else if (nv <= 8)  rms_norm_fwd_warp_kernel<8><<<wgrid, 256, 0, s>>>(X, W, O, rms_out, rows, D, eps);
+    else if (nv <= 16) rms_norm_fwd_warp_kernel<16><<<wgrid, 256, 0, s>>>(X, W, O, rms_out, rows, D, eps);
+    else if (D / 8 <= 128 * kMaxVec) rms_norm_fwd_kernel<128><<<grid, 128, 0, s>>>(X, W, O, rms_out, rows, D, eps);
     else                        rms_norm_fwd_kernel<256><<<grid, 256, 0, s>>>(X, W, O, rms_out, rows, D, eps);
     TA_LAUNCH_CHECK(ctx, "rms_norm_fwd_kernel");
     return TA_OK;
@@ -427,7 +540,12 @@ int ta_rms_norm_bwd(ta_ctx* ctx, const void* dy, const void* x, const void* w, c
     auto W = static_cast<const __nv_bfloat16*>(w);
     auto DX = static_cast<__nv_bfloat16*>(dx);
     auto AT = static_cast<const __nv_bfloat16*>(add_to);
-    if (D / 8 <= 128 * kMaxVec) rms_norm_bwd_kernel<128><<<grid, 128, 0, s>>>(DY, X, W, rms_saved, DX, AT, rows, D);
+    const int nv = (D / 8 + 31) / 32;
+    const unsigned wgrid = unsigned(std::min<long>((rows + 7) / 8, long(ctx->sm_count) * 8));
+    if (nv <= 4)       rms_norm_bwd_warp_kernel<4><<<wgrid, 256, 0, s>>>(DY, X, W, rms_saved, DX, AT, rows, D);
+    else if (nv <= 8)  rms_norm_bwd_warp_kernel<8><<<wgrid, 256, 0, s>>>(DY, X, W, rms_saved, DX, AT, rows, D);
+    else if (nv <= 16) rms_norm_bwd_warp_kernel<16><<<wgrid, 256, 0, s>>>(DY, X, W, rms_saved, DX, AT, rows, D);
+    else if (D / 8 <= 128 * kMaxVec) rms_norm_bwd_kernel<128><<<grid, 128, 0, s>>>(DY, X, W, rms_saved, DX, AT, rows, D);
     else                        rms_norm_bwd_kernel<256><<<grid, 256, 0, s>>>(DY, X, W, rms_saved, DX, AT, rows, D);
     TA_LAUNCH_CHECK(ctx, "rms_norm_bwd_kernel");
     return TA_OK;

@@ -355,8 +355,9 @@ TileChoice pick_tile(int M, int N, double ksum, bool any_a_mn, int sms) {
     if (N <= 32) return {32, 1};
     if (N <= 64) return {64, 1};
     struct Cand { int bn, mh; double eff, fixed; };
-    static const Cand cands[] = {{256, 2, 0.84, 2600}, {224, 2, 0.82, 2400}, {256, 1, 0.70, 400},
-                                 {224, 1, 0.68, 400},  {128, 1, 0.52, 300},  {64, 1, 0.30, 250}};
+    // eff = measured (tile FLOPs / 8192 per clock) / (clocks per tile) on 16384-row problems, K >= 3584
+    static const Cand cands[] = {{256, 2, 0.645, 2600}, {224, 2, 0.63, 2400}, {256, 1, 0.53, 400},
+                                 {224, 1, 0.50, 400},   {128, 1, 0.31, 300},  {64, 1, 0.18, 250}};
     if (const char* f = std::getenv("TA_GEMM_TILE")) {   // tuning knob: "BN,MH" forces one tile shape
         int bn = 0, mh = 0;
         if (std::sscanf(f, "%d,%d", &bn, &mh) == 2 && (mh == 1 || (mh == 2 && !any_a_mn && M >= 256)) &&
