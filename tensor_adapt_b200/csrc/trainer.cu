@@ -91,8 +91,20 @@ void target_dims(const ta_model_config& c, int t, int* in, int* out) {
 #define RC(call) do { if (int _rc = (call)) return _rc; } while (0)
 
 // y = x.W^T (+bias) (+ s.h.B^T) (+residual); keeps h_s in the layer cache for the backward
+// h_s of every projection of a fused group in ONE pass over x: the A blocks of the group are contiguous
+// in the working array ([n*r][in]) and the result is [BT][n*r], of which each projection owns a slice.
+int lora_down_group(ta_trainer* t, int l, int first_tgt, int n, const bf16* x, int BT) {
+    LoraRef lr = t->ref(l, first_tgt);
+    LoraSlot& sl = t->slot(l, first_tgt);
+    GemmSegment g;
+    g.A = x; g.lda = sl.in; g.B = lr.A; g.ldb = sl.in; g.K = sl.in;
+    GemmOut o;
+    o.C = t->cache[l].h[first_tgt]; o.ldc = sl.h_ld; o.alpha = t->scale;
+    return seg_gemm(t->ctx, t->stream, BT, n * lr.r, &g, 1, o);
+}
+
 int proj_fwd(ta_trainer* t, int l, int tgt, const bf16* x, const bf16* W, const bf16* bias, const bf16* residual,
-             bf16* y, int BT) {
+             bf16* y, int BT, bool h_ready = false) {
     int in, out;
     target_dims(t->mc, tgt, &in, &out);
     GemmSegment seg[2];
@@ -101,8 +113,8 @@ int proj_fwd(ta_trainer* t, int l, int tgt, const bf16* x, const bf16* W, const 
     LoraRef lr = t->ref(l, tgt);
     if (lr.on()) {
         bf16* h = t->cache[l].h[tgt];
-        RC(lora_down(t->ctx, t->stream, x, BT, in, lr, t->scale, h));
-        seg[1].A = h; seg[1].lda = lr.r; seg[1].B = lr.B; seg[1].ldb = lr.r; seg[1].K = lr.r;
+        if (!h_ready) RC(lora_down(t->ctx, t->stream, x, BT, in, lr, t->scale, h));
+        seg[1].A = h; seg[1].lda = t->slot(l, tgt).h_ld; seg[1].B = lr.B; seg[1].ldb = lr.r; seg[1].K = lr.r;
         nseg = 2;
     }
     GemmOut o;
@@ -113,7 +125,9 @@ int proj_fwd(ta_trainer* t, int l, int tgt, const bf16* x, const bf16* W, const 
 struct BwdProj { const bf16* dY; const bf16* W; int tgt; };
 
 // dX = sum_i dY_i.W_i + sum_i dh_i.A_i in ONE segmented GEMM; gA_i, gB_i accumulated on the way.
-int proj_bwd_group(ta_trainer* t, int l, const bf16* x, const BwdProj* ps, int np, bf16* dX, int BT) {
+// `fused`: the projections share x and form a fused group (contiguous A / gA blocks, dh slices of one
+// [BT][np*r] buffer), so gA of the whole group is one pass over x.
+int proj_bwd_group(ta_trainer* t, int l, const bf16* x, const BwdProj* ps, int np, bf16* dX, int BT, bool fused) {
     GemmSegment seg[kMaxSegments];
     int nseg = 0, in = 0;
     for (int i = 0; i < np; i++) {
@@ -122,32 +136,42 @@ int proj_bwd_group(ta_trainer* t, int l, const bf16* x, const BwdProj* ps, int n
         GemmSegment& g = seg[nseg++];
         g.A = ps[i].dY; g.lda = out; g.B = ps[i].W; g.ldb = in; g.b_mn = true; g.K = out;
     }
+    const int r = t->r_pad;
     for (int i = 0; i < np; i++) {
         LoraRef lr = t->ref(l, ps[i].tgt);
         if (!lr.on()) continue;
         int out;
         target_dims(t->mc, ps[i].tgt, &in, &out);
-        bf16* dh = t->dh[i];
+        const int dh_ld = fused ? np * r : r;
+        bf16* dh = fused ? t->dh[0] + i * r : t->dh[i];
         const bf16* h = t->cache[l].h[ps[i].tgt];
+        const int h_ld = t->slot(l, ps[i].tgt).h_ld;
         {   // dh_s = bf16(s.dY.B)
             GemmSegment g; g.A = ps[i].dY; g.lda = out; g.B = lr.B; g.ldb = lr.r; g.b_mn = true; g.K = out;
-            GemmOut o; o.C = dh; o.ldc = lr.r; o.alpha = t->scale;
+            GemmOut o; o.C = dh; o.ldc = dh_ld; o.alpha = t->scale;
             RC(seg_gemm(t->ctx, t->stream, BT, lr.r, &g, 1, o));
         }
         {   // gB += dY^T.h_s
-            GemmSegment g; g.A = ps[i].dY; g.lda = out; g.a_mn = true; g.B = h; g.ldb = lr.r; g.b_mn = true; g.K = BT;
+            GemmSegment g; g.A = ps[i].dY; g.lda = out; g.a_mn = true; g.B = h; g.ldb = h_ld; g.b_mn = true; g.K = BT;
             GemmOut o; o.C = lr.gB; o.ldc = lr.r; o.f32 = true; o.accumulate = true;
             o.split_k = tokens_gemm_splits(t->ctx, out, lr.r, BT); o.split_ws = t->splitk; o.split_ws_bytes = t->splitk_bytes;
             RC(seg_gemm(t->ctx, t->stream, out, lr.r, &g, 1, o));
         }
-        {   // gA += dh_s^T.x (tiles [in][r], stored transposed)
-            GemmSegment g; g.A = x; g.lda = in; g.a_mn = true; g.B = dh; g.ldb = lr.r; g.b_mn = true; g.K = BT;
+        if (!fused) {   // gA += dh_s^T.x (tiles [in][r], stored transposed)
+            GemmSegment g; g.A = x; g.lda = in; g.a_mn = true; g.B = dh; g.ldb = dh_ld; g.b_mn = true; g.K = BT;
             GemmOut o; o.C = lr.gA; o.ldc = in; o.f32 = true; o.accumulate = true; o.transpose_out = true;
             o.split_k = tokens_gemm_splits(t->ctx, in, lr.r, BT); o.split_ws = t->splitk; o.split_ws_bytes = t->splitk_bytes;
             RC(seg_gemm(t->ctx, t->stream, in, lr.r, &g, 1, o));
         }
         GemmSegment& g = seg[nseg++];
-        g.A = dh; g.lda = lr.r; g.B = lr.A; g.ldb = in; g.b_mn = true; g.K = lr.r;
+        g.A = dh; g.lda = dh_ld; g.B = lr.A; g.ldb = in; g.b_mn = true; g.K = lr.r;
+    }
+    if (fused) {   // gA of the whole group: [in][np*r] tiles stored transposed into the contiguous gA blocks
+        LoraRef first = t->ref(l, ps[0].tgt);
+        GemmSegment g; g.A = x; g.lda = in; g.a_mn = true; g.B = t->dh[0]; g.ldb = np * r; g.b_mn = true; g.K = BT;
+        GemmOut o; o.C = first.gA; o.ldc = in; o.f32 = true; o.accumulate = true; o.transpose_out = true;
+        o.split_k = tokens_gemm_splits(t->ctx, in, np * r, BT); o.split_ws = t->splitk; o.split_ws_bytes = t->splitk_bytes;
+        RC(seg_gemm(t->ctx, t->stream, in, np * r, &g, 1, o));
     }
     GemmOut o;
     o.C = dX; o.ldc = in;
@@ -169,15 +193,17 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count) {
         LayerCache& k = t->cache[l];
         bf16* r_next = (l + 1 < Lyr) ? t->cache[l + 1].r_in : t->r_final;
         RC(ta_rms_norm_fwd(ctx, k.r_in, w.input_norm, k.x_normed, k.in_rms, BT, H, c.rms_eps, s));
-        RC(proj_fwd(t, l, T_Q, k.x_normed, w.q_w, w.q_b, nullptr, k.Q, BT));
-        RC(proj_fwd(t, l, T_K, k.x_normed, w.k_w, w.k_b, nullptr, k.K, BT));
-        RC(proj_fwd(t, l, T_V, k.x_normed, w.v_w, w.v_b, nullptr, k.V, BT));
+        if (t->fuse_qkv) RC(lora_down_group(t, l, T_Q, 3, k.x_normed, BT));
+        RC(proj_fwd(t, l, T_Q, k.x_normed, w.q_w, w.q_b, nullptr, k.Q, BT, t->fuse_qkv));
+        RC(proj_fwd(t, l, T_K, k.x_normed, w.k_w, w.k_b, nullptr, k.K, BT, t->fuse_qkv));
+        RC(proj_fwd(t, l, T_V, k.x_normed, w.v_w, w.v_b, nullptr, k.V, BT, t->fuse_qkv));
         RC(ta_rope(ctx, k.Q, c.q_heads, k.K, c.kv_heads, Bm, T, c.head_dim, c.rope_theta, 0, s));
         RC(ta_flash_attn_fwd(ctx, k.Q, k.K, k.V, k.attn_out, k.lse, Bm, T, c.q_heads, c.kv_heads, c.head_dim, s));
         RC(proj_fwd(t, l, T_O, k.attn_out, w.o_w, nullptr, k.r_in, k.r_mid, BT));          // + residual
         RC(ta_rms_norm_fwd(ctx, k.r_mid, w.post_norm, k.x_normed2, k.post_rms, BT, H, c.rms_eps, s));
-        RC(proj_fwd(t, l, T_GATE, k.x_normed2, w.gate_w, nullptr, nullptr, k.gate, BT));
-        RC(proj_fwd(t, l, T_UP, k.x_normed2, w.up_w, nullptr, nullptr, k.up, BT));
+        if (t->fuse_gu) RC(lora_down_group(t, l, T_GATE, 2, k.x_normed2, BT));
+        RC(proj_fwd(t, l, T_GATE, k.x_normed2, w.gate_w, nullptr, nullptr, k.gate, BT, t->fuse_gu));
+        RC(proj_fwd(t, l, T_UP, k.x_normed2, w.up_w, nullptr, nullptr, k.up, BT, t->fuse_gu));
         RC(ta_silu_mul_fwd(ctx, k.gate, k.up, k.act, long(BT) * I, s));
         RC(proj_fwd(t, l, T_DOWN, k.act, w.down_w, nullptr, k.r_mid, r_next, BT));         // + residual
     }
@@ -204,25 +230,25 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count) {
         LayerCache& k = t->cache[l];
         {   // FFN: dact = grad.Wd (+LoRA down)                                (qwen2.cu:221-225)
             BwdProj p{t->g_res, w.down_w, T_DOWN};
-            RC(proj_bwd_group(t, l, k.act, &p, 1, t->d_act, BT));
+            RC(proj_bwd_group(t, l, k.act, &p, 1, t->d_act, BT, false));
         }
         RC(ta_silu_mul_bwd(ctx, t->d_act, k.gate, k.up, t->d_gate, t->d_up, long(BT) * I, s));
         {   // dx_normed2 = dgate.Wg + dup.Wu (+LoRA)                           (:232-234)
             BwdProj p[2] = {{t->d_gate, w.gate_w, T_GATE}, {t->d_up, w.up_w, T_UP}};
-            RC(proj_bwd_group(t, l, k.x_normed2, p, 2, t->d_xn, BT));
+            RC(proj_bwd_group(t, l, k.x_normed2, p, 2, t->d_xn, BT, t->fuse_gu));
         }
         // grad += rms_norm_bwd(dx_normed2, pre_ffn_res)                       (:238-246)
         RC(ta_rms_norm_bwd(ctx, t->d_xn, k.r_mid, w.post_norm, k.post_rms, t->g_res, t->g_res, BT, H, s));
         {   // dx_attn_out = grad.Wo (+LoRA o)                                 (:253-264)
             BwdProj p{t->g_res, w.o_w, T_O};
-            RC(proj_bwd_group(t, l, k.attn_out, &p, 1, t->d_attn, BT));
+            RC(proj_bwd_group(t, l, k.attn_out, &p, 1, t->d_attn, BT, false));
         }
         RC(ta_flash_attn_bwd(ctx, t->d_attn, k.Q, k.K, k.V, k.attn_out, k.lse, t->dQ, t->dK, t->dV, t->delta, Bm, T,
                              c.q_heads, c.kv_heads, c.head_dim, s));
         RC(ta_rope(ctx, t->dQ, c.q_heads, t->dK, c.kv_heads, Bm, T, c.head_dim, c.rope_theta, 1, s));
         {   // dx_normed = dQ.Wq + dK.Wk + dV.Wv (+LoRA q,k,v)                  (:282-292)
             BwdProj p[3] = {{t->dQ, w.q_w, T_Q}, {t->dK, w.k_w, T_K}, {t->dV, w.v_w, T_V}};
-            RC(proj_bwd_group(t, l, k.x_normed, p, 3, t->d_xn, BT));
+            RC(proj_bwd_group(t, l, k.x_normed, p, 3, t->d_xn, BT, t->fuse_qkv));
         }
         // centroid side-channel: hidden = x_normed, signal = dx_normed        (adapt_trainer.cu:210-232)
         if (t->ac.centroid_modes & 1)
@@ -294,19 +320,34 @@ int ta_trainer_create(ta_ctx* ctx, const ta_model_config* mc, const ta_adapter_c
             w.up_w = static_cast<bf16*>(W.take(bytes_bf16(I * H)));
             w.down_w = static_cast<bf16*>(W.take(bytes_bf16(H * I)));
         }
-        // LoRA slots: offsets in elements, each block padded to 128 elements
+        // LoRA slots: offsets in elements, each block padded to 128 elements.  Projections that read the
+        // same input (q/k/v, gate/up) get their A blocks back to back - and, as all five arrays share the
+        // offsets, their gA blocks too - so one GEMM serves the whole group.
         t->slots.assign(size_t(Lyr) * T_COUNT, LoraSlot());
+        auto on = [&](int tg) { return (ac->targets & (1 << tg)) != 0; };
+        t->fuse_qkv = on(T_Q) && on(T_K) && on(T_V);
+        t->fuse_gu = on(T_GATE) && on(T_UP);
         long off = 0;
         size_t sk_need = 0;
+        static const int kGroups[4][3] = {{T_Q, T_K, T_V}, {T_O, -1, -1}, {T_GATE, T_UP, -1}, {T_DOWN, -1, -1}};
         for (int l = 0; l < Lyr; l++)
-            for (int tg = 0; tg < T_COUNT; tg++) {
-                if (!(ac->targets & (1 << tg))) continue;
-                LoraSlot& sl = t->slot(l, tg);
-                sl.on = true;
-                target_dims(c, tg, &sl.in, &sl.out);
-                sl.offA = off; off += (long(r) * sl.in + 127) / 128 * 128;
-                sl.offB = off; off += (long(sl.out) * r + 127) / 128 * 128;
-                sk_need = std::max({sk_need, tokens_gemm_ws_bytes_max(ctx, sl.out, r), tokens_gemm_ws_bytes_max(ctx, sl.in, r)});
+            for (const auto& grp : kGroups) {
+                int members[3], nm = 0;
+                for (int tg : grp) if (tg >= 0 && on(tg)) members[nm++] = tg;
+                const bool fused = (grp[0] == T_Q && t->fuse_qkv) || (grp[0] == T_GATE && t->fuse_gu);
+                for (int i = 0; i < nm; i++) {   // all A blocks of the group first ...
+                    LoraSlot& sl = t->slot(l, members[i]);
+                    sl.on = true;
+                    target_dims(c, members[i], &sl.in, &sl.out);
+                    sl.h_ld = fused ? nm * r : r;
+                    sl.offA = off; off += (long(r) * sl.in + 127) / 128 * 128;
+                }
+                for (int i = 0; i < nm; i++) {   // ... then the B blocks
+                    LoraSlot& sl = t->slot(l, members[i]);
+                    sl.offB = off; off += (long(sl.out) * r + 127) / 128 * 128;
+                    sk_need = std::max({sk_need, tokens_gemm_ws_bytes_max(ctx, sl.out, r),
+                                        tokens_gemm_ws_bytes_max(ctx, sl.in, fused ? nm * r : r)});
+                }
             }
         t->lora_n = off;
         t->master = static_cast<float*>(Lo.take(size_t(off) * 4));
@@ -337,8 +378,18 @@ int ta_trainer_create(ta_ctx* ctx, const ta_model_config* mc, const ta_adapter_c
             k.in_rms = static_cast<float*>(A.take(size_t(BT) * 4));
             k.post_rms = static_cast<float*>(A.take(size_t(BT) * 4));
             k.lse = static_cast<float*>(A.take(size_t(BT) * c.q_heads * 4));
+            for (int tg = 0; tg < T_COUNT; tg++) k.h[tg] = nullptr;
+            if (t->fuse_qkv) {
+                bf16* hb = static_cast<bf16*>(A.take(bytes_bf16(BT * 3 * r)));
+                k.h[T_Q] = hb; k.h[T_K] = hb ? hb + r : nullptr; k.h[T_V] = hb ? hb + 2 * r : nullptr;
+            }
+            if (t->fuse_gu) {
+                bf16* hb = static_cast<bf16*>(A.take(bytes_bf16(BT * 2 * r)));
+                k.h[T_GATE] = hb; k.h[T_UP] = hb ? hb + r : nullptr;
+            }
             for (int tg = 0; tg < T_COUNT; tg++)
-                k.h[tg] = t->slot(l, tg).on ? static_cast<bf16*>(A.take(bytes_bf16(BT * r))) : nullptr;
+                if (t->slot(l, tg).on && !k.h[tg] && !((tg <= T_V && t->fuse_qkv) || ((tg == T_GATE || tg == T_UP) && t->fuse_gu)))
+                    k.h[tg] = static_cast<bf16*>(A.take(bytes_bf16(BT * r)));
         }
         t->r_final = static_cast<bf16*>(A.take(bytes_bf16(BT * H)));
         t->x_final_normed = static_cast<bf16*>(A.take(bytes_bf16(BT * H)));
@@ -355,7 +406,10 @@ int ta_trainer_create(ta_ctx* ctx, const ta_model_config* mc, const ta_adapter_c
         t->dQ = static_cast<bf16*>(A.take(bytes_bf16(BT * qd)));
         t->dK = static_cast<bf16*>(A.take(bytes_bf16(BT * kv)));
         t->dV = static_cast<bf16*>(A.take(bytes_bf16(BT * kv)));
-        for (int i = 0; i < 3; i++) t->dh[i] = static_cast<bf16*>(A.take(bytes_bf16(BT * r)));
+        {   // one [BT][3r] block: separate projections use r-wide thirds, a fused group uses slices of it
+            bf16* db = static_cast<bf16*>(A.take(bytes_bf16(BT * 3 * r)));
+            for (int i = 0; i < 3; i++) t->dh[i] = db ? db + long(i) * BT * r : nullptr;
+        }
         t->delta = static_cast<float*>(A.take(size_t(BT) * c.q_heads * 4));
         t->splitk_bytes = sk_need + 256;
         t->splitk = static_cast<float*>(A.take(t->splitk_bytes));

@@ -18,6 +18,7 @@ struct LoraSlot {
     bool on = false;
     int in = 0, out = 0;
     long offA = 0, offB = 0;   // element offsets into the flat LoRA arrays (shared by all five arrays)
+    int h_ld = 0;              // row pitch of this projection's h_s / dh_s slice (r, or n*r inside a fused group)
 };
 
 struct LayerW {
@@ -69,6 +70,8 @@ struct ta_trainer {
     __nv_bfloat16* dh[3] = {nullptr, nullptr, nullptr};
     float *delta = nullptr, *splitk = nullptr, *loss = nullptr;
     size_t splitk_bytes = 0;
+    int dh_ld[3] = {0, 0, 0};
+    bool fuse_qkv = false, fuse_gu = false;   // projections sharing an input share one h / dh / gA pass
     int* tok = nullptr;
     int* tgt = nullptr;
     int logit_rows = 0;       // rows of the lm-head chunk buffer

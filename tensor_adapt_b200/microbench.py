@@ -5,6 +5,7 @@ with ncu; the summaries under profiles/ name the exact command lines).
     python -m tensor_adapt_b200.microbench gemm --M 16384 --N 3584 --K 3584 [--b-layout 1]
     python -m tensor_adapt_b200.microbench rowops --rows 16384 --D 3584 --I 18944
     python -m tensor_adapt_b200.microbench lora --BT 4096 --in 896 --out 896 --rank 16
+    python -m tensor_adapt_b200.microbench skinny --BT 16384 --in 3584 --out 18944 --rank 16
 
 Each line reports the median of `--iters` launches after `--warmup`; inputs are larger than L2 or the
 L2 is flushed between launches (a 256 MB buffer is rewritten) when `--flush` is given.
@@ -89,6 +90,27 @@ def lora(ctx, a):
            shape=[BT, ind, od, r])
 
 
+def skinny(ctx, a):
+    """The four rank-r products of one adapted projection, each HBM-bound: bytes = the big operand once."""
+    BT, ind, od, r = a.BT, getattr(a, "in"), a.out, a.rank
+    x, dY = rnd(BT, ind), rnd(BT, od)
+    A, Bm = rnd(r, ind, scale=0.03), rnd(od, r, scale=0.02)
+    h = torch.empty(BT, r, device="cuda", dtype=torch.bfloat16); dh = torch.empty_like(h)
+    gA = torch.zeros(r, ind, device="cuda"); gB = torch.zeros(od, r, device="cuda")
+    t = timeit(lambda: ctx.call("ta_gemm_bf16", BT, r, ind, 2.0, ptr(x), ind, 0, ptr(A), ind, 0, None, None, ptr(h), r, stream_ptr()),
+               a.iters, a.warmup, a.flush)
+    report("h = x.A^T", t, bytes_=2.0 * BT * ind, shape=[BT, ind, r])
+    t = timeit(lambda: ctx.call("ta_gemm_bf16", BT, r, od, 2.0, ptr(dY), od, 0, ptr(Bm), r, 1, None, None, ptr(dh), r, stream_ptr()),
+               a.iters, a.warmup, a.flush)
+    report("dh = dY.B", t, bytes_=2.0 * BT * od, shape=[BT, od, r])
+    t = timeit(lambda: ctx.call("ta_gemm_tokens_f32", od, r, BT, 1.0, ptr(dY), od, ptr(h), r, ptr(gB), r, 1, 0, stream_ptr()),
+               a.iters, a.warmup, a.flush)
+    report("gB += dY^T.h", t, bytes_=2.0 * BT * (od + r), shape=[od, r, BT])
+    t = timeit(lambda: ctx.call("ta_gemm_tokens_f32", ind, r, BT, 1.0, ptr(x), ind, ptr(dh), r, ptr(gA), ind, 1, 1, stream_ptr()),
+               a.iters, a.warmup, a.flush)
+    report("gA += dh^T.x", t, bytes_=2.0 * BT * (ind + r), shape=[ind, r, BT])
+
+
 def rowops(ctx, a):
     rows, D, I = a.rows, a.D, a.I
     x, w, dy = rnd(rows, D), rnd(D), rnd(rows, D)
@@ -116,7 +138,7 @@ def rowops(ctx, a):
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention", "gemm", "lora", "rowops"):
+    for name in ("attention", "gemm", "lora", "rowops", "skinny"):
         s = sub.add_parser(name)
         s.add_argument("--iters", type=int, default=10); s.add_argument("--warmup", type=int, default=3)
         s.add_argument("--flush", action="store_true")
@@ -127,7 +149,7 @@ def main():
             for k, v in (("M", 16384), ("N", 3584), ("K", 3584)):
                 s.add_argument("--" + k, type=int, default=v)
             s.add_argument("--b-layout", type=int, default=0)
-        elif name == "lora":
+        elif name in ("lora", "skinny"):
             for k, v in (("BT", 4096), ("in", 896), ("out", 896), ("rank", 16)):
                 s.add_argument("--" + k, type=int, default=v)
         else:
@@ -135,7 +157,7 @@ def main():
                 s.add_argument("--" + k, type=int, default=v)
     a = ap.parse_args()
     ctx = ta.Context(0)
-    {"attention": attention, "gemm": gemm, "lora": lora, "rowops": rowops}[a.what](ctx, a)
+    {"attention": attention, "gemm": gemm, "lora": lora, "rowops": rowops, "skinny": skinny}[a.what](ctx, a)
     torch.cuda.synchronize()
     ctx.check_device()
 
