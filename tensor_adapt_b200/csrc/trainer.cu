@@ -496,6 +496,7 @@ int ta_trainer_tensor(ta_trainer* t, const char* name, void** dev_ptr, long* row
     else if (n == "lora.m") set(t->m, 1, t->lora_n, 0);
     else if (n == "lora.v") set(t->v, 1, t->lora_n, 0);
     else if (n == "lora.working") set(t->working, 1, t->lora_n, 1);
+    else if (n == "step.stats") set(t->stats, 1, 4, 0);   // [grad norm, clip scale, loss sum, loss count]
     else if (n == "centroid.acc") set(t->cen_acc, 1, H, 0);
     else if (n == "centroid.weight") set(t->cen_w, 1, 1, 0);
     else if (n == "centroid_asbuilt.acc") set(t->cen_acc_ab, 1, H, 0);

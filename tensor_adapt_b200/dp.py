@@ -33,18 +33,40 @@ def allreduce_sum_(tensors, group=None):
 
 
 class DataParallelStep:
-    """zero_grad -> local forward/backward on this rank's shard -> all-reduce -> optimiser step."""
+    """zero_grad -> local forward/backward on this rank's shard -> all-reduce -> optimiser step.
 
-    def __init__(self, trainer, rank: int, world: int):
-        self.tr, self.rank, self.world = trainer, rank, world
+    Reduced per step: the flat LoRA gradient array and the (loss sum, loss count) pair, so every rank
+    reports the global-batch mean loss of src/trainer/adapt_trainer.cu:237-246.  Reduced per snapshot:
+    the centroid sums (`write_snapshot`); each rank keeps its own running sums in between."""
+
+    def __init__(self, trainer, rank: int, world: int, group=None):
+        self.tr, self.rank, self.world, self.group = trainer, rank, world, group
         self.grad = trainer.torch_view("lora.grad")
-        p, _, n, _, _ = trainer.tensor("centroid.weight")
-        self._stats = None
+        self.stats = trainer.torch_view("step.stats")
 
     def step(self, tokens, targets, global_batch: int, lr: float = -1.0, total_steps: int = 0):
         tr = self.tr
         tok, tgt, b_local = shard_batch(tokens, targets, global_batch, tr.seq_len, self.rank, self.world)
         tr.zero_grad()
         tr.forward_backward(tok, tgt, b_local, global_tokens=global_batch * tr.seq_len)
-        allreduce_sum_([self.grad])
+        allreduce_sum_([self.grad, self.stats[2:4]], self.group)
         return tr.optimizer_step(lr, total_steps)
+
+    def write_snapshot(self, step: int, mode: int = 0):
+        """CentroidAccumulator::write_snapshot (src/centroid/centroid_accumulator.cpp:72-91) over the
+        whole job: the per-rank sums are added (sums commute), every rank normalises the same global
+        centroid and keeps it for the final merge, only rank 0 writes the file."""
+        tr = self.tr
+        names = ("centroid.acc", "centroid.weight") if mode == 0 else ("centroid_asbuilt.acc", "centroid_asbuilt.weight")
+        views = [tr.torch_view(n) for n in names]
+        local = [v.clone() for v in views]
+        allreduce_sum_(views, self.group)
+        out_dir = tr.output_dir
+        if self.rank != 0:
+            tr.output_dir = None
+        try:
+            return tr.write_snapshot(step, mode)
+        finally:
+            tr.output_dir = out_dir
+            for v, l in zip(views, local):
+                v.copy_(l)

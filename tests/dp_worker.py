@@ -31,8 +31,12 @@ def main(out_path):
     for s in range(2):
         m = dp.step(toks[s], tgts[s], B, lr=2e-4)
         out[f"gnorm{s}"] = np.float32(m.grad_norm_raw)
+        out[f"loss{s}"] = np.float32(m.loss)
         out[f"master{s}"] = tr.download("lora.master")
     out["grad_last"] = tr.download("lora.grad")
+    out["centroid"], out["centroid_w"] = dp.write_snapshot(2)
+    out["centroid_w"] = np.float32(out["centroid_w"])
+    out["local_w_after"] = tr.download("centroid.weight")   # the rank's own sums survive the snapshot
     ctx.check_device()
     if rank == 0:
         np.savez(out_path, **out)

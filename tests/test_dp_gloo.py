@@ -63,3 +63,62 @@ def test_two_rank_data_parallel_equals_single_process(tmp_path):
     assert abs(z["stats"][0] - float(loss.sum())) <= 1e-4 * float(loss.sum()) and z["stats"][1] == B * T
     ref_c = np.concatenate([cen.acc, cen.weight])
     assert np.abs(z["cen"] - ref_c).max() <= 1e-3 * np.abs(ref_c).max()
+
+
+class _FakeTrainer:
+    """Host-side stand-in with the attributes DataParallelStep touches (CPU tensors instead of HBM)."""
+
+    def __init__(self, rank, out_dir):
+        self.seq_len, self.rank, self.output_dir = 4, rank, out_dir
+        self.t = {"lora.grad": torch.zeros(6), "step.stats": torch.zeros(4), "centroid.acc": torch.zeros(3),
+                  "centroid.weight": torch.zeros(1)}
+        self.written = []
+
+    def torch_view(self, name):
+        return self.t[name]
+
+    def zero_grad(self):
+        self.t["lora.grad"].zero_(); self.t["step.stats"].zero_()
+
+    def forward_backward(self, tok, tgt, b_local, global_tokens=0):
+        self.t["lora.grad"] += float(np.sum(tok)) / global_tokens
+        self.t["step.stats"][2] += float(np.sum(tgt)); self.t["step.stats"][3] += len(tgt)
+        self.t["centroid.acc"] += self.rank + 1.0; self.t["centroid.weight"] += 2.0
+
+    def optimizer_step(self, lr, total_steps):
+        s = self.t["step.stats"]
+        return float(s[2] / s[3]), self.t["lora.grad"].clone()
+
+    def write_snapshot(self, step, mode=0):
+        self.written.append(self.output_dir)
+        return (self.t["centroid.acc"] / self.t["centroid.weight"]).numpy().copy(), float(self.t["centroid.weight"])
+
+
+def _dp_step_main(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    from tensor_adapt_b200.dp import DataParallelStep
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    tr = _FakeTrainer(rank, out_dir)
+    dp = DataParallelStep(tr, rank, world)
+    toks = np.arange(16, dtype=np.int32); tgts = np.arange(16, dtype=np.int32) * 2
+    loss, grad = dp.step(toks, tgts, global_batch=4)
+    cen, w = dp.write_snapshot(1)
+    np.savez(os.path.join(out_dir, f"r{rank}.npz"), loss=loss, grad=grad.numpy(), cen=cen, w=w,
+             local_w=tr.t["centroid.weight"].numpy(), wrote=np.array([d is not None for d in tr.written]),
+             out_dir_kept=np.array(tr.output_dir == out_dir))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_data_parallel_step_reduces_grads_loss_and_snapshot(tmp_path):
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_dp_step_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    z0, z1 = np.load(tmp_path / "r0.npz"), np.load(tmp_path / "r1.npz")
+    for z in (z0, z1):
+        assert float(z["loss"]) == pytest.approx(np.arange(16).sum() * 2 / 16)      # global mean on every rank
+        np.testing.assert_allclose(z["grad"], np.full(6, np.arange(16).sum() / 16.0), rtol=1e-6)
+        np.testing.assert_allclose(z["cen"], np.full(3, 3.0 / 4.0))                  # (1 + 2) / (2 + 2)
+        assert float(z["w"]) == 4.0 and float(z["local_w"][0]) == 2.0                # local sums restored
+        assert bool(z["out_dir_kept"])
+    assert z0["wrote"].tolist() == [True] and z1["wrote"].tolist() == [False]        # only rank 0 gets a path

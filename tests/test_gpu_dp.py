@@ -1,6 +1,7 @@
 """Data parallelism on real GPUs: a 2-rank NCCL run (torchrun, one process per GPU) of two optimiser
 steps must give the single-GPU result on the same global batch - the LoRA gradients differ only by
-FP32 reduction order, so masters agree to 1e-6 and the gradient norm to 1e-5 relative.
+FP32 reduction order, so masters agree to 1e-6 and the gradient norm to 1e-5 relative; the reported loss is the global-batch
+mean and the job-wide centroid snapshot equals the single-GPU one.
 Skipped when fewer than two GPUs are visible."""
 import os
 import subprocess
@@ -35,9 +36,13 @@ def test_two_gpu_step_equals_single_gpu(ctx, tmp_path):
     for s in range(2):
         m = tr.step(toks[s], tgts[s], B, lr=2e-4)
         assert abs(m.grad_norm_raw - float(z[f"gnorm{s}"])) <= 1e-4 * m.grad_norm_raw
+        assert abs(m.loss - float(z[f"loss{s}"])) <= 1e-5 * abs(m.loss)          # global-batch mean on every rank
         # Adam's sign-like first steps can flip on near-zero gradients: allow a few 2*lr outliers
         d = np.abs(tr.download("lora.master") - z[f"master{s}"])
         assert np.mean(d > 1e-6) < 1e-3 and d.max() <= 2.2 * 2e-4 * (s + 1)
     g = tr.download("lora.grad")
     assert rc.cosine(g, z["grad_last"]) >= 0.99999
+    cen, w = tr.write_snapshot(2)
+    assert abs(w - float(z["centroid_w"])) <= 1e-4 * w and float(z["local_w_after"].ravel()[0]) < 0.9 * w
+    assert np.linalg.norm(cen - z["centroid"]) <= 1e-4 * np.linalg.norm(cen)
     tr.close()
