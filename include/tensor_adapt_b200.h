@@ -288,6 +288,37 @@ int ta_trainer_set_meta(ta_trainer* tr, const char* arch_name, const char* base_
  * (centroid_accumulator.cpp:93-168 as called from AdaptTrainer::save_adapter, adapt_trainer.cu:322-325). */
 int ta_trainer_merge_snapshots(ta_trainer* tr, int k, const char* out_path, int* passes);
 
+/* ── real weights and resume ─────────────────────────────────────────────────────────────── */
+/* parser::ModelConfig::from_dir + the derived fields of base::BaseLoader::load
+ * (src/parser/config.cpp:43-110,132-134; src/base/base_loader.cpp:90-110,160): reads <dir>/config.json with
+ * the reference's defaults, head_dim = hidden / heads, tie_embeddings = the shards hold no
+ * "lm_head.weight"; arch_name = "model_type"; sha_hex = SHA-256 of the "name:size;" listing of the
+ * directory's *.safetensors files sorted by name (base_loader.cpp:30-52). Host only, no GPU needed.
+ * TA_ERR_IO (unreadable / malformed files, text in err_text) or TA_ERR_UNSUPPORTED (architecture
+ * neither qwen* nor llama*, after applying arch_hint like detect_arch, base_loader.cpp:21-28). */
+int ta_base_probe(const char* dir, const char* arch_hint, ta_model_config* mc, char* arch_name, int arch_cap, char* sha_hex,
+                  int sha_cap, char* err_text, int err_cap);
+/* base::BaseLoader::load (src/base/base_loader.cpp:80-170) into the trainer's weight arena: shard
+ * discovery as parser::WeightMap::open (src/parser/weight_map.cpp:26-68: a .safetensors file, else
+ * <dir>/model.safetensors alone, else every *.safetensors by name), header validation as
+ * parser::SafeTensors (src/parser/safetensors.cpp:86-226), Hugging Face tensor names, BF16 copied as is,
+ * F32 rounded to BF16 (RNE), any other dtype refused (TA_ERR_UNSUPPORTED) like upload_bf16
+ * (base_loader.cpp:54-74). Unlike the reference, element counts are checked against the config. Also
+ * sets the architecture / base_sha that adapter.json records. */
+int ta_trainer_load_base(ta_trainer* tr, const char* dir, const char* arch_hint);
+/* Writes <dir>/optimizer.safetensors: FP32 masters, AdamW m and v (the flat arrays), both centroid
+ * accumulators, step and tokens_consumed. The reference documents this file (README.md:569-582) but has
+ * no code for it: no reference counterpart. */
+int ta_trainer_save_optimizer(ta_trainer* tr, const char* dir);
+/* Resume (README.md:646-661; absent from the reference's code): validates <dir>/adapter.json (rank,
+ * alpha, base_sha) against this trainer, then restores masters / moments / centroid sums / step / tokens
+ * from optimizer.safetensors, or - for a checkpoint the reference wrote - masters from the BF16
+ * adapter.safetensors with zero moments and step / tokens from train_state.json. */
+int ta_trainer_resume(ta_trainer* tr, const char* dir);
+/* Optimiser steps taken and tokens consumed so far (StepMetrics::step / tokens_consumed,
+ * include/tensor/trainer/adapt_trainer.hpp), e.g. after ta_trainer_resume. */
+int ta_trainer_counters(ta_trainer* tr, long* step, long* tokens_consumed);
+
 /* ── host-side logic mirrored from the reference ─────────────────────────────────────────── */
 /* CosineSchedule::lr_at (include/tensor/trainer/cosine_schedule.hpp:18-29). */
 float ta_cosine_lr(float base_lr, long warmup_steps, long total_steps, long step, float floor_frac);

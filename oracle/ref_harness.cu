@@ -25,6 +25,7 @@
 #include <tensor/backend/cuda/ops.hpp>
 #include <tensor/backend/cuda/tensor.hpp>
 #include <tensor/base/arch/qwen2.hpp>
+#include <tensor/base/base_loader.hpp>
 #include <tensor/base/frozen_base.hpp>
 #include <tensor/centroid/centroid_accumulator.hpp>
 #include <tensor/checkpoint/adapter_writer.hpp>
@@ -443,14 +444,46 @@ static int mode_trainer(const std::string& dir, const std::string& out) {
     return 0;
 }
 
+// ───────────────────────── mode: load ─────────────────────────
+// BaseLoader::load on a Hugging Face style directory; dumps the derived config and every tensor
+// (BF16 bits) so that the package's loader can be compared with it.
+
+static int mode_load(const std::string& dir, const std::string& out) {
+    Device dev = Device::open("cuda:0");
+    base::FrozenBase b = base::BaseLoader::load(dir, dev);
+    fs::create_directories(out);
+    const base::BaseConfig& c = b.config;
+    std::ofstream f(out + "/config.txt");
+    f.precision(9);
+    f << "arch_name " << c.arch_name << "\nbase_sha " << c.base_sha << "\nvocab " << c.vocab_size << "\nhidden "
+      << c.hidden_size << "\nlayers " << c.num_layers << "\nhq " << c.num_q_heads << "\nhkv " << c.num_kv_heads
+      << "\nhd " << c.head_dim << "\ninter " << c.intermediate_size << "\neps " << c.rms_norm_eps << "\ntheta "
+      << c.rope_theta << "\ntie " << (c.tie_embeddings ? 1 : 0) << "\n";
+    dump_tensor(out + "/embed.bin", b.embed_w);
+    dump_tensor(out + "/final_norm.bin", b.final_norm_w);
+    if (!c.tie_embeddings) dump_tensor(out + "/lm_head.bin", b.lm_head_w);
+    for (std::size_t l = 0; l < b.layers.size(); l++) {
+        const base::LayerWeights& w = b.layers[l];
+        const std::string p = out + "/l" + std::to_string(l) + "_";
+        dump_tensor(p + "input_norm.bin", w.input_norm_w); dump_tensor(p + "post_norm.bin", w.post_norm_w);
+        dump_tensor(p + "q_w.bin", w.q_proj_w); dump_tensor(p + "q_b.bin", w.q_proj_b);
+        dump_tensor(p + "k_w.bin", w.k_proj_w); dump_tensor(p + "k_b.bin", w.k_proj_b);
+        dump_tensor(p + "v_w.bin", w.v_proj_w); dump_tensor(p + "v_b.bin", w.v_proj_b);
+        dump_tensor(p + "o_w.bin", w.o_proj_w); dump_tensor(p + "gate_w.bin", w.gate_proj_w);
+        dump_tensor(p + "up_w.bin", w.up_proj_w); dump_tensor(p + "down_w.bin", w.down_proj_w);
+    }
+    return 0;
+}
+
 int main(int argc, char** argv) {
-    if (argc < 3) { std::cerr << "usage: ref_harness <op|step|trainer|bench> <case_dir> [out_dir]\n"; return 2; }
+    if (argc < 3) { std::cerr << "usage: ref_harness <op|step|trainer|bench|load> <case_dir> [out_dir]\n"; return 2; }
     std::string mode = argv[1], dir = argv[2], out = argc > 3 ? argv[3] : dir + "/out";
     try {
         if (mode == "op")      return mode_op(dir, out);
         if (mode == "step")    return mode_step(dir, out, false);
         if (mode == "bench")   return mode_step(dir, out, true);
         if (mode == "trainer") return mode_trainer(dir, out);
+        if (mode == "load")    return mode_load(dir, out);
     } catch (const std::exception& e) {
         std::cerr << "ref_harness: " << e.what() << "\n";
         return 1;

@@ -684,6 +684,71 @@ def safetensors_bytes(adapter) -> bytes:
     return struct.pack("<Q", len(hdr)) + hdr.encode() + bytes(data)
 
 
+HF_LAYER_NAMES = {   # BaseLoader::load's tensor names (src/base/base_loader.cpp:112-160)
+    "input_norm": "input_layernorm.weight", "post_norm": "post_attention_layernorm.weight",
+    "q_w": "self_attn.q_proj.weight", "q_b": "self_attn.q_proj.bias", "k_w": "self_attn.k_proj.weight",
+    "k_b": "self_attn.k_proj.bias", "v_w": "self_attn.v_proj.weight", "v_b": "self_attn.v_proj.bias",
+    "o_w": "self_attn.o_proj.weight", "gate_w": "mlp.gate_proj.weight", "up_w": "mlp.up_proj.weight",
+    "down_w": "mlp.down_proj.weight"}
+
+
+def hf_tensor_dict(base) -> Dict[str, np.ndarray]:
+    """The frozen base under the Hugging Face names BaseLoader::load asks for."""
+    d = {"model.embed_tokens.weight": base["embed"], "model.norm.weight": base["final_norm"]}
+    if "lm_head" in base:
+        d["lm_head.weight"] = base["lm_head"]
+    for l, lw in enumerate(base["layers"]):
+        for k, name in HF_LAYER_NAMES.items():
+            d[f"model.layers.{l}.{name}"] = lw[k]
+    return d
+
+
+def write_safetensors_file(path: str, tensors: Dict[str, np.ndarray], f32_names=(), metadata=None) -> None:
+    """A safetensors file in the published layout (u64 LE header length | JSON | data): F32 arrays
+    are stored as BF16 (their values must already be BF16-representable) unless named in f32_names."""
+    hdr, data = {}, bytearray()
+    if metadata:
+        hdr["__metadata__"] = metadata
+    for name, a in tensors.items():
+        if name in f32_names:
+            b, dt = np.ascontiguousarray(a, dtype="<f4").tobytes(), "F32"
+        else:
+            b, dt = bf16_bits(np.ascontiguousarray(a, dtype=F32).reshape(-1)).astype("<u2").tobytes(), "BF16"
+        hdr[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [len(data), len(data) + len(b)]}
+        data += b
+    txt = json.dumps(hdr, separators=(",", ":"))
+    while len(txt) % 8:
+        txt += " "
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(txt)) + txt.encode() + bytes(data))
+
+
+def write_hf_dir(d: str, cfg: "BaseConfig", base, shards: int = 1, f32_names=(), model_type: str = "qwen2") -> None:
+    """config.json + model.safetensors (or model-0000i-of-0000n.safetensors shards, split round-robin)
+    as BaseLoader::load / WeightMap::open expect them (src/parser/weight_map.cpp:26-68)."""
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump({"architectures": ["Qwen2ForCausalLM"], "model_type": model_type, "vocab_size": cfg.vocab,
+                   "hidden_size": cfg.hidden, "num_hidden_layers": cfg.layers, "num_attention_heads": cfg.hq,
+                   "num_key_value_heads": cfg.hkv, "intermediate_size": cfg.inter, "rms_norm_eps": cfg.eps,
+                   "rope_theta": cfg.theta, "tie_word_embeddings": bool(cfg.tie), "torch_dtype": "bfloat16"}, f, indent=2)
+    t = hf_tensor_dict(base)
+    if shards == 1:
+        write_safetensors_file(os.path.join(d, "model.safetensors"), t, f32_names, {"format": "pt"})
+        return
+    names = list(t)
+    for i in range(shards):
+        part = {n: t[n] for n in names[i::shards]}
+        write_safetensors_file(os.path.join(d, f"model-{i + 1:05d}-of-{shards:05d}.safetensors"), part, f32_names, {"format": "pt"})
+
+
+def base_sha(d: str) -> str:
+    """sha256_dir (src/base/base_loader.cpp:30-52): SHA-256 of "name:size;" over the sorted *.safetensors."""
+    import hashlib
+    names = sorted(n for n in os.listdir(d) if n.endswith(".safetensors"))
+    return hashlib.sha256("".join(f"{n}:{os.path.getsize(os.path.join(d, n))};" for n in names).encode()).hexdigest()
+
+
 def _nlohmann_float(x: float) -> str:
     """nlohmann::json number_float dump: shortest round-trip of the double, '.0' appended when the
     text looks like an integer."""

@@ -84,6 +84,11 @@ _PROTOS = {
     "ta_trainer_write_snapshot": (c_int, [P, c_int, c_char_p, P, P]),
     "ta_trainer_save_checkpoint": (c_int, [P, c_char_p, c_char_p, c_long, c_long, c_int]),
     "ta_trainer_set_meta": (c_int, [P, c_char_p, c_char_p]),
+    "ta_base_probe": (c_int, [c_char_p, c_char_p, P, c_char_p, c_int, c_char_p, c_int, c_char_p, c_int]),
+    "ta_trainer_load_base": (c_int, [P, c_char_p, c_char_p]),
+    "ta_trainer_save_optimizer": (c_int, [P, c_char_p]),
+    "ta_trainer_resume": (c_int, [P, c_char_p]),
+    "ta_trainer_counters": (c_int, [P, POINTER(c_long), POINTER(c_long)]),
     "ta_trainer_merge_snapshots": (c_int, [P, c_int, c_char_p, POINTER(c_int)]),
     "ta_cosine_lr": (c_float, [c_float, c_long, c_long, c_long, c_float]),
     "ta_mask_targets": (None, [P, P, c_int, c_int]),

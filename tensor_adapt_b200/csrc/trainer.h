@@ -70,7 +70,6 @@ struct ta_trainer {
     __nv_bfloat16* dh[3] = {nullptr, nullptr, nullptr};
     float *delta = nullptr, *splitk = nullptr, *loss = nullptr;
     size_t splitk_bytes = 0;
-    int dh_ld[3] = {0, 0, 0};
     bool fuse_qkv = false, fuse_gu = false;   // projections sharing an input share one h / dh / gA pass
     int* tok = nullptr;
     int* tgt = nullptr;

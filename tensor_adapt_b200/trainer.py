@@ -14,7 +14,7 @@ from typing import Optional
 
 import numpy as np
 
-from ._lib import Context, TAError, lib
+from ._lib import Context, TAError, lib  # noqa: F401
 
 TARGET_BITS = {"q": 1, "k": 2, "v": 4, "o": 8, "gate": 16, "up": 32, "down": 64}
 TARGETS_QKVO = 15
@@ -50,6 +50,17 @@ QWEN2 = {
     "qwen2-1.5b": ModelConfig(151936, 1536, 28, 12, 2, 128, 8960, 1e-6, 1e6, 1),
     "qwen2-7b": ModelConfig(152064, 3584, 28, 28, 4, 128, 18944, 1e-6, 1e6, 0),
 }
+
+
+def probe_base(directory: str, arch_hint: str = ""):
+    """(ModelConfig, model_type, base_sha) of a Hugging Face model directory, as BaseLoader::load derives
+    them (src/base/base_loader.cpp:90-110); host only."""
+    mc = ModelConfig()
+    arch, sha, err = ctypes.create_string_buffer(64), ctypes.create_string_buffer(65), ctypes.create_string_buffer(512)
+    rc = lib.ta_base_probe(directory.encode(), arch_hint.encode(), ctypes.byref(mc), arch, 64, sha, 65, err, 512)
+    if rc != 0:
+        raise TAError(rc, err.value.decode(errors="replace"))
+    return mc, arch.value.decode(), sha.value.decode()
 
 
 def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
@@ -132,6 +143,21 @@ class AdaptTrainer:
     def sync_working(self) -> None:
         self._call("ta_trainer_sync_working")
 
+    def load_base(self, directory: str, arch_hint: str = "") -> None:
+        """BaseLoader::load (src/base/base_loader.cpp:80-170): config.json + safetensors shards of a
+        Hugging Face checkpoint into the frozen-weight arena."""
+        self._call("ta_trainer_load_base", directory.encode(), arch_hint.encode())
+
+    def save_optimizer(self, directory: str) -> None:
+        self._call("ta_trainer_save_optimizer", directory.encode())
+
+    def resume(self, directory: str) -> None:
+        """Restore masters, AdamW moments, centroid sums, step and token counters from a checkpoint."""
+        self._call("ta_trainer_resume", directory.encode())
+        st, tk = c_long(0), c_long(0)
+        self._call("ta_trainer_counters", ctypes.byref(st), ctypes.byref(tk))
+        self.step_count, self.tokens_seen = st.value, tk.value
+
     def set_meta(self, arch_name: str, base_sha: str) -> None:
         self._call("ta_trainer_set_meta", arch_name.encode(), base_sha.encode())
 
@@ -186,9 +212,13 @@ class AdaptTrainer:
         self._call("ta_trainer_write_snapshot", mode, path, cen.ctypes.data_as(c_void_p), ctypes.byref(w))
         return cen, w.value
 
-    def save_checkpoint(self, directory: str) -> None:
+    def save_checkpoint(self, directory: str, with_optimizer: bool = True) -> None:
+        """AdapterWriter::save_checkpoint files, plus optimizer.safetensors (what `resume` needs for an
+        exact continuation)."""
         self._call("ta_trainer_save_checkpoint", directory.encode(), self.domain.encode(), self.step_count,
                    self.tokens_seen, 0)
+        if with_optimizer:
+            self.save_optimizer(directory)
 
     def save_adapter(self, directory: str, k: int = 16) -> None:
         """AdaptTrainer::save_adapter (adapt_trainer.cu:319-330): snapshot, k-means merge of the

@@ -12,6 +12,8 @@ Run on a machine with a B200 and the compiled reference (oracle/_ref, built by `
                       (adapter.safetensors, adapter.json, train_state.json)
   ref_op_cfg2.npz     BASELINE config 2 single LoRA-linear op (4096 x 896 -> 896, r16, alpha 32):
                       seed + reference outputs gA, gB in full and every 32nd row of y, dX (BF16 bits)
+  ref_load_tiny.json  BaseLoader::load on the seeded model directory of tests/refcase.py hf_case(): the
+                      derived config, base_sha and the SHA-256 of every loaded tensor's BF16 bytes
   kmeans_cfg1.npz     BASELINE config 1 k-means through the reference CLI oracle/_ref/centroid-merge:
                       vector order as the reference enumerated it + merged centres (runs without a GPU)
 """
@@ -108,14 +110,30 @@ def make_kmeans(out):
     shutil.rmtree(d)
 
 
+def make_load(out):
+    import hashlib
+    import json
+    d = tempfile.mkdtemp()
+    cfg, _ = rc.hf_case(os.path.join(d, "hf"))
+    rc.run_harness("load", os.path.join(d, "hf"), os.path.join(d, "ref"))
+    conf = dict(l.split(None, 1) for l in open(os.path.join(d, "ref", "config.txt")).read().splitlines())
+    hashes = {n[:-4]: hashlib.sha256(open(os.path.join(d, "ref", n), "rb").read()).hexdigest()
+              for n in sorted(os.listdir(os.path.join(d, "ref"))) if n.endswith(".bin")}
+    with open(os.path.join(out, "ref_load_tiny.json"), "w") as f:
+        json.dump({"config": conf, "sha256_of_bf16_bytes": hashes}, f, indent=1, sort_keys=True)
+    shutil.rmtree(d)
+
+
 if __name__ == "__main__":
     out = sys.argv[1] if len(sys.argv) > 1 else HERE
     os.makedirs(out, exist_ok=True)
-    which = sys.argv[2:] or ["kmeans", "step", "op"]
+    which = sys.argv[2:] or ["kmeans", "step", "op", "load"]
     if "kmeans" in which:
         make_kmeans(out)
     if "step" in which:
         make_step(out)
     if "op" in which:
         make_op(out)
+    if "load" in which:
+        make_load(out)
     print("golden fixtures written to", out)

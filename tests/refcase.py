@@ -93,3 +93,16 @@ def cosine(a, b):
 
 def relmax(a, b):
     return float(np.abs(np.asarray(a) - np.asarray(b)).max() / (np.abs(b).max() + 1e-30))
+
+
+def hf_case(d, shards=2, seed=17):
+    """Seeded Hugging Face style model directory (untied head, two F32 tensors whose values need rounding)
+    shared by tests/golden/make_golden.py and the loader tests; returns (cfg, base)."""
+    cfg = tiny_cfg(hidden=128, hq=2, hkv=1, hd=64, inter=256, vocab=320, layers=2)
+    cfg.tie = False
+    rng = np.random.default_rng(seed)
+    base = o.make_base(cfg, rng, std=0.05, norm_jitter=0.1)
+    base["layers"][1]["v_w"] = (rng.standard_normal(base["layers"][1]["v_w"].shape) * 0.05).astype(np.float32)
+    base["lm_head"] = (rng.standard_normal(base["lm_head"].shape) * 0.05).astype(np.float32)
+    o.write_hf_dir(d, cfg, base, shards=shards, f32_names={"model.layers.1.self_attn.v_proj.weight", "lm_head.weight"})
+    return cfg, base
