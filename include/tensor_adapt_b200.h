@@ -319,6 +319,30 @@ int ta_trainer_resume(ta_trainer* tr, const char* dir);
  * include/tensor/trainer/adapt_trainer.hpp), e.g. after ta_trainer_resume. */
 int ta_trainer_counters(ta_trainer* tr, long* step, long* tokens_consumed);
 
+/* ── token stream in HBM ─────────────────────────────────────────────────────────────────── */
+typedef struct ta_dataset ta_dataset;
+/* data::Dataset::load (src/data/dataset.cpp:15-53): a .bin file or a directory of .bin files (sorted by
+ * path) of 32-bit token ids, concatenated - here into device memory, once. */
+int ta_dataset_load(ta_ctx* ctx, const char* path, ta_dataset** out);
+int ta_dataset_destroy(ta_dataset* ds);
+/* Dataset::total_tokens / tokens_consumed and the read position (include/tensor/data/dataset.hpp). */
+int ta_dataset_info(const ta_dataset* ds, long* total_tokens, long* position, long* tokens_consumed);
+/* Restores the read position on resume (README.md:646-661 "continues ... same data position"); no
+ * reference code. */
+int ta_dataset_seek(ta_dataset* ds, long position, long tokens_consumed);
+/* Dataset::next_batch (src/data/dataset.cpp:55-71) on the device: B windows of T tokens from the read
+ * position with wrap-around, targets = the next token; the position advances by B*T. Only sequences
+ * [first_seq, first_seq + n_seq) are materialised (a data-parallel rank's shard of the global batch)
+ * into ids_dev / targets_dev [n_seq*T]. mask != 0 also applies the assistant-only target masking of
+ * src/trainer/adapt_trainer.cu:145-182 in the same kernel. */
+int ta_dataset_next_batch(ta_dataset* ds, int B, int T, int first_seq, int n_seq, int* ids_dev, int* targets_dev, int mask,
+                          cudaStream_t stream);
+/* The masking alone (src/trainer/adapt_trainer.cu:145-182) on device arrays; ta_mask_targets is the host form. */
+int ta_mask_targets_device(ta_ctx* ctx, const int* input_ids, int* target_ids, int B, int T, cudaStream_t stream);
+/* AdaptTrainer::step as the reference runs it (do_step, src/trainer/adapt_trainer.cu:130-277: next_batch,
+ * masking, zero_grad, forward, loss, backward, centroid, clip, AdamW) with the batch drawn on the device. */
+int ta_trainer_step_dataset(ta_trainer* tr, ta_dataset* ds, int B, int mask, float lr, long total_steps, ta_step_metrics* out);
+
 /* ── host-side logic mirrored from the reference ─────────────────────────────────────────── */
 /* CosineSchedule::lr_at (include/tensor/trainer/cosine_schedule.hpp:18-29). */
 float ta_cosine_lr(float base_lr, long warmup_steps, long total_steps, long step, float floor_frac);

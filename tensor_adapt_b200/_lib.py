@@ -88,6 +88,13 @@ _PROTOS = {
     "ta_trainer_load_base": (c_int, [P, c_char_p, c_char_p]),
     "ta_trainer_save_optimizer": (c_int, [P, c_char_p]),
     "ta_trainer_resume": (c_int, [P, c_char_p]),
+    "ta_dataset_load": (c_int, [P, c_char_p, POINTER(c_void_p)]),
+    "ta_dataset_destroy": (c_int, [P]),
+    "ta_dataset_info": (c_int, [P, POINTER(c_long), POINTER(c_long), POINTER(c_long)]),
+    "ta_dataset_seek": (c_int, [P, c_long, c_long]),
+    "ta_dataset_next_batch": (c_int, [P, c_int, c_int, c_int, c_int, P, P, c_int, P]),
+    "ta_mask_targets_device": (c_int, [P, P, P, c_int, c_int, P]),
+    "ta_trainer_step_dataset": (c_int, [P, P, c_int, c_int, c_float, c_long, P]),
     "ta_trainer_counters": (c_int, [P, POINTER(c_long), POINTER(c_long)]),
     "ta_trainer_merge_snapshots": (c_int, [P, c_int, c_char_p, POINTER(c_int)]),
     "ta_cosine_lr": (c_float, [c_float, c_long, c_long, c_long, c_float]),

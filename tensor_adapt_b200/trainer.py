@@ -63,6 +63,46 @@ def probe_base(directory: str, arch_hint: str = ""):
     return mc, arch.value.decode(), sha.value.decode()
 
 
+class Dataset:
+    """data::Dataset (include/tensor/data/dataset.hpp) with the token stream resident in HBM."""
+
+    def __init__(self, ctx: Context, path: str):
+        self.ctx, h = ctx, c_void_p()
+        ctx.call("ta_dataset_load", path.encode(), ctypes.byref(h))
+        self.h = h
+
+    def _info(self):
+        a, b, c = c_long(0), c_long(0), c_long(0)
+        lib.ta_dataset_info(self.h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+        return a.value, b.value, c.value
+
+    total_tokens = property(lambda self: self._info()[0])
+    position = property(lambda self: self._info()[1])
+    tokens_consumed = property(lambda self: self._info()[2])
+
+    def seek(self, position: int, tokens_consumed: int = 0) -> None:
+        lib.ta_dataset_seek(self.h, position, tokens_consumed)
+
+    def next_batch(self, B: int, T: int, ids_ptr, targets_ptr, first_seq: int = 0, n_seq: int = -1, mask: bool = True,
+                   stream=None) -> None:
+        """Fills device arrays (pointers) with sequences [first_seq, first_seq+n_seq) of the next global batch."""
+        rc = lib.ta_dataset_next_batch(self.h, B, T, first_seq, B - first_seq if n_seq < 0 else n_seq, ids_ptr, targets_ptr,
+                                       int(mask), stream)
+        if rc != 0:
+            raise TAError(rc, (lib.ta_last_error(self.ctx.h) or b"").decode())
+
+    def close(self) -> None:
+        if self.h:
+            lib.ta_dataset_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
     return ((u + (((u >> 16) & 1) + np.uint32(0x7FFF))) >> 16).astype(np.uint16)
@@ -195,6 +235,13 @@ class AdaptTrainer:
         if self.output_dir and self.checkpoint_every and m.step % self.checkpoint_every == 0:
             self.write_snapshot(m.step)
             self.save_checkpoint(os.path.join(self.output_dir, f"step-{m.step}"))
+        return m
+
+    def step_dataset(self, ds: "Dataset", B: int, mask: bool = True, lr: float = -1.0, total_steps: int = 0) -> StepMetrics:
+        """AdaptTrainer::step with the batch drawn and masked on the device (no host arrays involved)."""
+        m = StepMetrics()
+        self._call("ta_trainer_step_dataset", ds.h, B, int(mask), lr, total_steps, ctypes.byref(m))
+        self.step_count, self.tokens_seen = m.step, m.tokens_consumed
         return m
 
     def done(self) -> bool:
