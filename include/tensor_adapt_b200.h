@@ -191,6 +191,19 @@ int ta_centroid_accumulate(ta_ctx* ctx, int mode, const void* hidden, const void
  * are host ints. Synchronises the stream once per pass (to read the "changed" flag). */
 int ta_kmeans_merge(ta_ctx* ctx, const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign,
                     int* k_out, int* passes_out, void* stream);
+/* The merge the README describes (README.md:73-79) but the reference does not implement: seeded
+ * k-means++ start (init_mode TA_KMEANS_INIT_PLUSPLUS: 64-bit LCG draws, FP32 distances in the order
+ * above, FP64 running sums for the pick - reproducible bit for bit) or the reference's even-spread
+ * start (TA_KMEANS_INIT_EVEN), the same Lloyd passes, then - if rank_by_mass - clusters reordered by
+ * descending summed gradient mass (mass [N] device FP32, NULL = count; FP64 sums, ties keep index
+ * order): centers and assign come back in ranked order / labels, cluster_mass [k] (device FP64, may be
+ * NULL) holds the masses, init_index [k] (device, may be NULL) the chosen start vectors. No
+ * reference counterpart. */
+#define TA_KMEANS_INIT_EVEN     0
+#define TA_KMEANS_INIT_PLUSPLUS 1
+int ta_kmeans_merge_ex(ta_ctx* ctx, const float* vectors, const float* mass, int N, int D, int k, int max_iters, int init_mode,
+                       unsigned long long seed, int rank_by_mass, float* centers, int* assign, double* cluster_mass,
+                       int* init_index, int* k_out, int* passes_out, void* stream);
 
 /* ── model / adapter / trainer ─────────────────────────────────────────────────────────────
  * The trainer object stands where the reference has FrozenBase + AdapterModel + AdamW +
@@ -354,6 +367,11 @@ void ta_kaiming_init_host(float* out, int in_dim, int rank, unsigned seed);
  * directory-iteration order, as the reference does), clusters on the GPU with ta_kmeans_merge and
  * writes int32 k | int32 D | k*D f32 to out_path. *n_vectors / *passes (may be NULL) report what ran. */
 int ta_centroid_merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, int k, int* n_vectors, int* passes);
+/* The same over ta_kmeans_merge_ex: seeded k-means++ start and / or the bank ordered by gradient mass,
+ * the mass of a snapshot being the trailing weight field of its file (README.md:73-79 "merged cluster
+ * bank, gradient-ranked"); same output layout. No reference counterpart. */
+int ta_centroid_merge_dir_ex(ta_ctx* ctx, const char* dir, const char* out_path, int k, int init_mode, unsigned long long seed,
+                             int rank_by_mass, int* n_vectors, int* passes);
 /* Host <-> device copies for callers without a CUDA runtime binding (synchronous). */
 int ta_memcpy_h2d(void* dst_dev, const void* src_host, size_t bytes);
 int ta_memcpy_d2h(void* dst_host, const void* src_dev, size_t bytes);

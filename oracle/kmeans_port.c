@@ -22,6 +22,8 @@
  *   - stop before the update when nothing changed     (:141)
  *   - update = sequential sum in n order, then `v /= count`; empty clusters stay all-zero (:144-156)
  * Returns the number of assignment passes executed. `centers` is [k*D], `assign` is [N]. */
+static int lloyd(const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign);
+
 int ta_oracle_kmeans(const float* vectors, int N, int D, int k, int max_iters,
                      float* centers, int* assign, int* k_out)
 {
@@ -29,6 +31,21 @@ int ta_oracle_kmeans(const float* vectors, int N, int D, int k, int max_iters,
     *k_out = k;
     for (int i = 0; i < k; i++)
         memcpy(centers + (size_t)i * D, vectors + (size_t)(((long)i * N) / k) * D, sizeof(float) * D);
+    return lloyd(vectors, N, D, k, max_iters, centers, assign);
+}
+
+/* The same Lloyd passes from caller-chosen starting centres vectors[init_idx[i]] (the seeded
+ * k-means++ extension; no reference counterpart). */
+int ta_oracle_kmeans_from(const float* vectors, int N, int D, int k, int max_iters, const int* init_idx,
+                          float* centers, int* assign)
+{
+    for (int i = 0; i < k; i++)
+        memcpy(centers + (size_t)i * D, vectors + (size_t)init_idx[i] * D, sizeof(float) * D);
+    return lloyd(vectors, N, D, k, max_iters, centers, assign);
+}
+
+static int lloyd(const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign)
+{
     for (int n = 0; n < N; n++) assign[n] = 0;
     int* counts = (int*)malloc(sizeof(int) * (k > 0 ? k : 1));
     int iters = 0;

@@ -530,6 +530,8 @@ def _kmeans_lib():
         fp = ctypes.POINTER(ctypes.c_float); ip = ctypes.POINTER(ctypes.c_int)
         _lib.ta_oracle_kmeans.argtypes = [fp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, fp, ip, ip]
         _lib.ta_oracle_kmeans.restype = ctypes.c_int
+        _lib.ta_oracle_kmeans_from.argtypes = [fp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ip, fp, ip]
+        _lib.ta_oracle_kmeans_from.restype = ctypes.c_int
         for f in (_lib.ta_oracle_centroid_intended, _lib.ta_oracle_centroid_asbuilt):
             f.argtypes = [fp, fp, ctypes.c_int, ctypes.c_int, fp, fp]
             f.restype = None
@@ -655,6 +657,27 @@ def rank_by_mass(assign: np.ndarray, mass: np.ndarray, k: int) -> np.ndarray:
     tot = np.zeros(k, dtype=np.float64)
     np.add.at(tot, assign, mass.astype(np.float64))
     return np.argsort(-tot, kind="stable").astype(np.int32)
+
+
+def kmeans_merge_ex(vectors: np.ndarray, mass: Optional[np.ndarray], k: int, seed: int, max_iters: int = 50):
+    """Extension pipeline: seeded k-means++ start, the reference's Lloyd passes, clusters reordered by
+    descending gradient mass. Returns (centers in ranked order, assignments in ranked labels, passes,
+    ranked cluster masses, chosen start indices)."""
+    v = np.ascontiguousarray(vectors, dtype=F32)
+    N, D = v.shape
+    kk = min(k, N)
+    idx = kmeans_pp_init(v, kk, seed)
+    centers = np.zeros((kk, D), dtype=F32)
+    assign = np.zeros(N, dtype=np.int32)
+    ip = ctypes.POINTER(ctypes.c_int)
+    it = _kmeans_lib().ta_oracle_kmeans_from(_fp(v), N, D, kk, max_iters, idx.ctypes.data_as(ip), _fp(centers),
+                                             assign.ctypes.data_as(ip))
+    m = np.ones(N, dtype=F32) if mass is None else np.asarray(mass, dtype=F32)
+    order = rank_by_mass(assign, m, kk)
+    tot = np.zeros(kk, dtype=np.float64)
+    np.add.at(tot, assign, m.astype(np.float64))
+    inv = np.empty(kk, dtype=np.int32); inv[order] = np.arange(kk, dtype=np.int32)
+    return centers[order], inv[assign], it, tot[order], idx
 
 
 # ───────────────────────────── checkpoint files ─────────────────────────────

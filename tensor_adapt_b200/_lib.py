@@ -88,6 +88,9 @@ _PROTOS = {
     "ta_trainer_load_base": (c_int, [P, c_char_p, c_char_p]),
     "ta_trainer_save_optimizer": (c_int, [P, c_char_p]),
     "ta_trainer_resume": (c_int, [P, c_char_p]),
+    "ta_kmeans_merge_ex": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, ctypes.c_ulonglong, c_int, P, P, P, P,
+                                   POINTER(c_int), POINTER(c_int), P]),
+    "ta_centroid_merge_dir_ex": (c_int, [P, c_char_p, c_char_p, c_int, c_int, ctypes.c_ulonglong, c_int, POINTER(c_int), POINTER(c_int)]),
     "ta_dataset_load": (c_int, [P, c_char_p, POINTER(c_void_p)]),
     "ta_dataset_destroy": (c_int, [P]),
     "ta_dataset_info": (c_int, [P, POINTER(c_long), POINTER(c_long), POINTER(c_long)]),

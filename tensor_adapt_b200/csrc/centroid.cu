@@ -193,6 +193,84 @@ __global__ void kmeans_update_kernel(const float* __restrict__ vec, const int* _
     centers[i] = count > 0 ? __fdiv_rn(c, float(count)) : 0.f;
 }
 
+// ── seeded k-means++ start and ranking by gradient mass (no reference code: README.md:73-79) ──
+
+// squared distance to the newest centre, same FP32 order as kmeans_dist_kernel; keeps the running minimum
+__global__ void kmeans_pp_dist_kernel(const float* __restrict__ vec, int N, int D, const int* __restrict__ chosen, int j,
+                                      float* __restrict__ d2) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    const float* x = vec + size_t(n) * D;
+    const float* c = vec + size_t(chosen[j]) * D;
+    float d = 0.f;
+    for (int i = 0; i < D; i++) {
+        const float v = __fsub_rn(x[i], c[i]);
+        d = __fadd_rn(d, __fmul_rn(v, v));
+    }
+    d2[n] = j == 0 ? d : fminf(d2[n], d);
+}
+
+// next centre: first index whose FP64 running sum of d2 exceeds u * total (one thread: the running
+// sum is order-dependent and N is the number of snapshots, not a hot loop)
+__global__ void kmeans_pp_pick_kernel(const float* __restrict__ d2, int N, double u, int* __restrict__ chosen, int j) {
+    if (blockIdx.x || threadIdx.x) return;
+    double total = 0.0;
+    for (int n = 0; n < N; n++) total = __dadd_rn(total, double(d2[n]));
+    const double r = __dmul_rn(u, total);
+    double run = 0.0;
+    int pick = N - 1;
+    for (int n = 0; n < N; n++) {
+        run = __dadd_rn(run, double(d2[n]));
+        if (run > r) { pick = n; break; }
+    }
+    chosen[j] = pick;
+}
+
+__global__ void kmeans_gather_kernel(const float* __restrict__ vec, int N, int D, int k, const int* __restrict__ chosen,
+                                     float* __restrict__ centers, int* __restrict__ assign) {
+    const long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+    if (i < long(k) * D) {
+        const int ki = int(i / D), d = int(i - long(ki) * D);
+        centers[i] = vec[size_t(chosen[ki]) * D + d];
+    }
+    if (i < N) assign[i] = 0;
+}
+
+// per-cluster FP64 mass in vector order, then a stable descending order of the clusters (k is small)
+__global__ void kmeans_rank_kernel(const int* __restrict__ assign, const float* __restrict__ mass, int N, int k,
+                                   double* __restrict__ tot, int* __restrict__ order, int* __restrict__ inverse) {
+    const int ki = threadIdx.x;
+    if (ki < k) {
+        double t = 0.0;
+        for (int n = 0; n < N; n++)
+            if (assign[n] == ki) t = __dadd_rn(t, mass ? double(mass[n]) : 1.0);
+        tot[ki] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < k; i++) order[i] = i;
+        for (int i = 1; i < k; i++) {   // insertion sort: equal masses keep their index order
+            const int o = order[i];
+            int j = i - 1;
+            while (j >= 0 && tot[order[j]] < tot[o]) { order[j + 1] = order[j]; j--; }
+            order[j + 1] = o;
+        }
+        for (int i = 0; i < k; i++) inverse[order[i]] = i;
+    }
+}
+
+__global__ void kmeans_permute_kernel(const float* __restrict__ centers_in, const double* __restrict__ tot_in, int D, int k, int N,
+                                      const int* __restrict__ order, const int* __restrict__ inverse,
+                                      float* __restrict__ centers_out, double* __restrict__ tot_out, int* __restrict__ assign) {
+    const long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+    if (i < long(k) * D) {
+        const int ki = int(i / D), d = int(i - long(ki) * D);
+        centers_out[i] = centers_in[size_t(order[ki]) * D + d];
+    }
+    if (i < k && tot_out) tot_out[i] = tot_in[order[i]];
+    if (i < N) assign[i] = inverse[assign[i]];
+}
+
 }  // namespace
 }  // namespace ta
 
@@ -229,20 +307,9 @@ int ta_centroid_accumulate(ta_ctx* ctx, int mode, const void* hidden, const void
     return TA_OK;
 }
 
-int ta_kmeans_merge(ta_ctx* ctx, const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign,
-                    int* k_out, int* passes_out, void* stream) {
-    if (!ctx || !vectors || !centers || !assign || N <= 0 || D <= 0 || k <= 0 || max_iters < 0)
-        return fail(ctx, TA_ERR_INVALID, "kmeans_merge: null argument or bad size");
-    k = std::min(k, N);
-    if (k_out) *k_out = k;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    void* ws = nullptr;
-    if (int rc = get_workspace(ctx, size_t(N) * k * sizeof(float) + 256, &ws)) return rc;
-    int* changed = static_cast<int*>(ws);
-    float* dist = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
-    const long ninit = std::max<long>(long(k) * D, N);
-    kmeans_init_kernel<<<unsigned((ninit + 255) / 256), 256, 0, s>>>(vectors, N, D, k, centers, assign);
-    TA_LAUNCH_CHECK(ctx, "kmeans_init_kernel");
+// Lloyd passes from the centres already in `centers` (assign starts at 0 everywhere)
+static int kmeans_lloyd(ta_ctx* ctx, const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign,
+                        int* changed, float* dist, int* passes_out, cudaStream_t s) {
     int passes = 0;
     for (int it = 0; it < max_iters; it++) {
         passes++;
@@ -259,6 +326,90 @@ int ta_kmeans_merge(ta_ctx* ctx, const float* vectors, int N, int D, int k, int 
         TA_LAUNCH_CHECK(ctx, "kmeans_update_kernel");
     }
     if (passes_out) *passes_out = passes;
+    return TA_OK;
+}
+
+int ta_kmeans_merge(ta_ctx* ctx, const float* vectors, int N, int D, int k, int max_iters, float* centers, int* assign,
+                    int* k_out, int* passes_out, void* stream) {
+    if (!ctx || !vectors || !centers || !assign || N <= 0 || D <= 0 || k <= 0 || max_iters < 0)
+        return fail(ctx, TA_ERR_INVALID, "kmeans_merge: null argument or bad size");
+    k = std::min(k, N);
+    if (k_out) *k_out = k;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    void* ws = nullptr;
+    if (int rc = get_workspace(ctx, size_t(N) * k * sizeof(float) + 256, &ws)) return rc;
+    int* changed = static_cast<int*>(ws);
+    float* dist = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
+    const long ninit = std::max<long>(long(k) * D, N);
+    kmeans_init_kernel<<<unsigned((ninit + 255) / 256), 256, 0, s>>>(vectors, N, D, k, centers, assign);
+    TA_LAUNCH_CHECK(ctx, "kmeans_init_kernel");
+    return kmeans_lloyd(ctx, vectors, N, D, k, max_iters, centers, assign, changed, dist, passes_out, s);
+}
+
+int ta_kmeans_merge_ex(ta_ctx* ctx, const float* vectors, const float* mass, int N, int D, int k, int max_iters, int init_mode,
+                       unsigned long long seed, int rank_by_mass, float* centers, int* assign, double* cluster_mass,
+                       int* init_index, int* k_out, int* passes_out, void* stream) {
+    if (!ctx || !vectors || !centers || !assign || N <= 0 || D <= 0 || k <= 0 || max_iters < 0 ||
+        (init_mode != TA_KMEANS_INIT_EVEN && init_mode != TA_KMEANS_INIT_PLUSPLUS))
+        return fail(ctx, TA_ERR_INVALID, "kmeans_merge_ex: null argument, bad size or unknown init mode");
+    k = std::min(k, N);
+    if (k > 1024) return fail(ctx, TA_ERR_UNSUPPORTED, "kmeans_merge_ex: at most 1024 clusters");
+    if (k_out) *k_out = k;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // workspace: changed flag | dist [N,k] | d2 [N] | chosen [k] | order [k] | inverse [k] | tot [k] f64 | centres copy [k,D]
+    auto al = [](size_t x) { return (x + 255) & ~size_t(255); };
+    const size_t o_dist = 256, o_d2 = o_dist + al(size_t(N) * k * 4), o_ch = o_d2 + al(size_t(N) * 4), o_ord = o_ch + al(size_t(k) * 4),
+                 o_inv = o_ord + al(size_t(k) * 4), o_tot = o_inv + al(size_t(k) * 4), o_cc = o_tot + al(size_t(k) * 8),
+                 total = o_cc + al(size_t(k) * D * 4);
+    void* ws = nullptr;
+    if (int rc = get_workspace(ctx, total, &ws)) return rc;
+    char* w = static_cast<char*>(ws);
+    int* changed = reinterpret_cast<int*>(w);
+    float* dist = reinterpret_cast<float*>(w + o_dist);
+    float* d2 = reinterpret_cast<float*>(w + o_d2);
+    int* chosen = reinterpret_cast<int*>(w + o_ch);
+    int* order = reinterpret_cast<int*>(w + o_ord);
+    int* inverse = reinterpret_cast<int*>(w + o_inv);
+    double* tot = reinterpret_cast<double*>(w + o_tot);
+    float* ccopy = reinterpret_cast<float*>(w + o_cc);
+    const long ninit = std::max<long>(long(k) * D, N);
+    if (init_mode == TA_KMEANS_INIT_EVEN) {
+        kmeans_init_kernel<<<unsigned((ninit + 255) / 256), 256, 0, s>>>(vectors, N, D, k, centers, assign);
+        TA_LAUNCH_CHECK(ctx, "kmeans_init_kernel");
+    } else {
+        // 64-bit LCG (Knuth's MMIX constants), 53-bit uniforms; the draws happen on the host, the
+        // distances and the picks on the device with no synchronisation in between
+        unsigned long long st = seed * 6364136223846793005ull + 1442695040888963407ull;
+        auto next_u = [&]() {
+            st = st * 6364136223846793005ull + 1442695040888963407ull;
+            return double(st >> 11) / 9007199254740992.0;
+        };
+        const int first = int(next_u() * N) % N;
+        TA_CUDA(ctx, cudaMemcpyAsync(chosen, &first, sizeof(int), cudaMemcpyHostToDevice, s));
+        TA_CUDA(ctx, cudaStreamSynchronize(s));   // `first` is a stack variable
+        for (int j = 1; j < k; j++) {
+            kmeans_pp_dist_kernel<<<(N + 127) / 128, 128, 0, s>>>(vectors, N, D, chosen, j - 1, d2);
+            TA_LAUNCH_CHECK(ctx, "kmeans_pp_dist_kernel");
+            kmeans_pp_pick_kernel<<<1, 32, 0, s>>>(d2, N, next_u(), chosen, j);
+            TA_LAUNCH_CHECK(ctx, "kmeans_pp_pick_kernel");
+        }
+        kmeans_gather_kernel<<<unsigned((ninit + 255) / 256), 256, 0, s>>>(vectors, N, D, k, chosen, centers, assign);
+        TA_LAUNCH_CHECK(ctx, "kmeans_gather_kernel");
+        if (init_index) TA_CUDA(ctx, cudaMemcpyAsync(init_index, chosen, size_t(k) * sizeof(int), cudaMemcpyDeviceToDevice, s));
+    }
+    if (int rc = kmeans_lloyd(ctx, vectors, N, D, k, max_iters, centers, assign, changed, dist, passes_out, s)) return rc;
+    if (rank_by_mass || cluster_mass) {
+        kmeans_rank_kernel<<<1, 1024, 0, s>>>(assign, mass, N, k, tot, order, inverse);
+        TA_LAUNCH_CHECK(ctx, "kmeans_rank_kernel");
+        if (rank_by_mass) {
+            TA_CUDA(ctx, cudaMemcpyAsync(ccopy, centers, size_t(k) * D * 4, cudaMemcpyDeviceToDevice, s));
+            kmeans_permute_kernel<<<unsigned((ninit + 255) / 256), 256, 0, s>>>(ccopy, tot, D, k, N, order, inverse, centers, cluster_mass,
+                                                                               assign);
+            TA_LAUNCH_CHECK(ctx, "kmeans_permute_kernel");
+        } else {
+            TA_CUDA(ctx, cudaMemcpyAsync(cluster_mass, tot, size_t(k) * 8, cudaMemcpyDeviceToDevice, s));
+        }
+    }
     return TA_OK;
 }
 

@@ -216,8 +216,15 @@ int ta_trainer_write_snapshot(ta_trainer* t, int mode, const char* path, float* 
     return TA_OK;
 }
 
+struct MergeOptions {
+    bool extended = false;           // seeded k-means++ / mass ranking instead of the reference's merge
+    int init_mode = 0, rank = 0;
+    unsigned long long seed = 0;
+    const std::vector<float>* mass = nullptr;
+};
+
 static int merge_vectors(ta_ctx* ctx, const std::vector<std::vector<float>>& snaps, int D, int k, const char* out_path,
-                         int* passes) {
+                         int* passes, const MergeOptions& mo = MergeOptions()) {
     const int N = int(snaps.size());
     std::vector<float> flat(size_t(N) * D);
     for (int n = 0; n < N; n++) std::memcpy(flat.data() + size_t(n) * D, snaps[size_t(n)].data(), size_t(D) * 4);
@@ -229,13 +236,23 @@ static int merge_vectors(ta_ctx* ctx, const std::vector<std::vector<float>>& sna
     TA_CUDA(ctx, cudaMalloc(&da, size_t(N) * 4));
     cudaMemcpy(dv, flat.data(), flat.size() * 4, cudaMemcpyHostToDevice);
     int kout = 0;
-    int rc = ta_kmeans_merge(ctx, dv, N, D, k, 50, dc, da, &kout, passes, nullptr);
+    int rc;
+    float* dm = nullptr;
+    if (mo.extended) {
+        if (mo.mass) {
+            TA_CUDA(ctx, cudaMalloc(&dm, size_t(N) * 4));
+            cudaMemcpy(dm, mo.mass->data(), size_t(N) * 4, cudaMemcpyHostToDevice);
+        }
+        rc = ta_kmeans_merge_ex(ctx, dv, dm, N, D, k, 50, mo.init_mode, mo.seed, mo.rank, dc, da, nullptr, nullptr, &kout, passes, nullptr);
+    } else {
+        rc = ta_kmeans_merge(ctx, dv, N, D, k, 50, dc, da, &kout, passes, nullptr);
+    }
     std::vector<float> centers(size_t(kk) * D);
     if (rc == TA_OK) {
         cudaStreamSynchronize(nullptr);
         cudaMemcpy(centers.data(), dc, centers.size() * 4, cudaMemcpyDeviceToHost);
     }
-    cudaFree(dv); cudaFree(dc); cudaFree(da);
+    cudaFree(dv); cudaFree(dc); cudaFree(da); cudaFree(dm);
     if (rc) return rc;
     std::ofstream f(out_path, std::ios::binary);
     if (!f) return fail(ctx, TA_ERR_IO, std::string("cannot write ") + out_path);
@@ -245,7 +262,7 @@ static int merge_vectors(ta_ctx* ctx, const std::vector<std::vector<float>>& sna
     return TA_OK;
 }
 
-int ta_centroid_merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, int k, int* n_vectors, int* passes) {
+static int merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, int k, int* n_vectors, int* passes, MergeOptions mo) {
     if (!ctx || !dir || !out_path || k <= 0) return fail(ctx, TA_ERR_INVALID, "centroid_merge_dir: bad argument");
     std::error_code ec;
     int D = 0;
@@ -258,6 +275,7 @@ int ta_centroid_merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, in
     }
     if (ec || D <= 0) return fail(ctx, TA_ERR_IO, std::string("No .centroid files in ") + dir);
     std::vector<std::vector<float>> snaps;
+    std::vector<float> mass;
     for (const auto& e : fs::directory_iterator(dir, ec)) {
         if (e.path().extension() != ".centroid") continue;
         std::ifstream f(e.path(), std::ios::binary);
@@ -266,11 +284,26 @@ int ta_centroid_merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, in
         if (d != D) continue;
         std::vector<float> c(size_t(d), 0.f);
         f.read(reinterpret_cast<char*>(c.data()), std::streamsize(size_t(d) * 4));
+        float w = 0.f;   // trailing accumulated gradient mass; the reference's merge never reads it
+        f.read(reinterpret_cast<char*>(&w), 4);
         snaps.push_back(std::move(c));
+        mass.push_back(w);
     }
     if (n_vectors) *n_vectors = int(snaps.size());
     if (snaps.empty()) return TA_OK;   // the reference logs "no snapshots to merge" and writes nothing
-    return merge_vectors(ctx, snaps, D, k, out_path, passes);
+    if (mo.extended) mo.mass = &mass;
+    return merge_vectors(ctx, snaps, D, k, out_path, passes, mo);
+}
+
+int ta_centroid_merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, int k, int* n_vectors, int* passes) {
+    return merge_dir(ctx, dir, out_path, k, n_vectors, passes, MergeOptions());
+}
+
+int ta_centroid_merge_dir_ex(ta_ctx* ctx, const char* dir, const char* out_path, int k, int init_mode, unsigned long long seed,
+                             int rank_by_mass, int* n_vectors, int* passes) {
+    MergeOptions mo;
+    mo.extended = true; mo.init_mode = init_mode; mo.seed = seed; mo.rank = rank_by_mass;
+    return merge_dir(ctx, dir, out_path, k, n_vectors, passes, mo);
 }
 
 int ta_trainer_merge_snapshots(ta_trainer* t, int k, const char* out_path, int* passes) {

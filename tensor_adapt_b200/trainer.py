@@ -290,6 +290,15 @@ class AdaptTrainer:
             pass
 
 
+def centroid_merge_ranked(ctx: Context, snapshot_dir: str, out_path: str, k: int = 16, seed: int = 0, plusplus: bool = True,
+                          rank_by_mass: bool = True):
+    """Seeded k-means++ merge with the bank ordered by gradient mass (README.md:73-79; extension)."""
+    n, passes = c_int(0), c_int(0)
+    ctx.call("ta_centroid_merge_dir_ex", snapshot_dir.encode(), out_path.encode(), k, int(plusplus), seed, int(rank_by_mass),
+             ctypes.byref(n), ctypes.byref(passes))
+    return n.value, passes.value
+
+
 def centroid_merge(ctx: Context, snapshot_dir: str, out_path: str, k: int = 16):
     """CentroidMerge::run (include/tensor/centroid/centroid_merge.hpp:12-19) on the GPU."""
     n = c_int(0); passes = c_int(0)

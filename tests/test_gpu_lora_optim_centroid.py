@@ -5,6 +5,7 @@ Tolerances (config 2's, from the north star): LoRA gradients cosine >= 0.999 and
 max|err| <= 2e-2 * max|ref|; BF16 activations max|err| <= 2e-2 * max|ref|; centroid vector relative
 L2 <= 1e-3; k-means assignments and centres bit-exact."""
 import ctypes
+import os
 
 import numpy as np
 import pytest
@@ -163,3 +164,51 @@ def test_kmeans_merge_bit_exact(ctx, N, D, k, seed):
     assert kout.value == kk and passes.value == ref_it
     assert np.array_equal(assign.cpu().numpy(), ref_a)
     assert centers.cpu().numpy().tobytes() == ref_c.tobytes()
+
+
+@pytest.mark.parametrize("N,D,k,seed", [(2048, 512, 8, 0), (100, 64, 16, 7), (5, 32, 8, 3), (513, 96, 3, 11)])
+def test_kmeans_plusplus_and_mass_ranking_bit_exact(ctx, N, D, k, seed):
+    """Extension (no reference code): seeded k-means++ start + Lloyd + ranking by gradient mass equals the
+    oracle's restatement bit for bit - chosen start vectors, centres, labels, FP64 cluster masses."""
+    if (N, D) == (2048, 512):
+        vec, mass = o.cfg1_vectors(seed)
+    else:
+        rng = np.random.default_rng(seed)
+        vec = rng.standard_normal((N, D)).astype(np.float32)
+        mass = rng.lognormal(0, 1, N).astype(np.float32)
+        vec[N // 2] = vec[0]                                            # duplicates: zero distances in the CDF
+    want_c, want_a, want_it, want_tot, want_idx = o.kmeans_merge_ex(vec, mass, k, seed)
+    kk = min(k, N)
+    vd, md = torch.from_numpy(vec).cuda(), torch.from_numpy(mass).cuda()
+    centers = torch.zeros(kk, D, device="cuda"); assign = torch.zeros(N, dtype=torch.int32, device="cuda")
+    tot = torch.zeros(kk, dtype=torch.float64, device="cuda"); idx = torch.zeros(kk, dtype=torch.int32, device="cuda")
+    kout, passes = ctypes.c_int(0), ctypes.c_int(0)
+    ctx.call("ta_kmeans_merge_ex", ptr(vd), ptr(md), N, D, k, 50, 1, seed, 1, ptr(centers), ptr(assign), ptr(tot), ptr(idx),
+             ctypes.byref(kout), ctypes.byref(passes), stream_ptr())
+    torch.cuda.synchronize()
+    assert kout.value == kk and passes.value == want_it
+    np.testing.assert_array_equal(idx.cpu().numpy(), want_idx)
+    np.testing.assert_array_equal(assign.cpu().numpy(), want_a)
+    np.testing.assert_array_equal(centers.cpu().numpy(), want_c)
+    np.testing.assert_array_equal(tot.cpu().numpy(), want_tot)
+    assert np.all(np.diff(tot.cpu().numpy()) <= 0)                      # ranked: heaviest cluster first
+    # even-spread start + no ranking through the same entry point == the reference-mode merge
+    ref_c, ref_a, ref_it = o.kmeans_merge(vec, k, 50)
+    ctx.call("ta_kmeans_merge_ex", ptr(vd), None, N, D, k, 50, 0, 0, 0, ptr(centers), ptr(assign), None, None,
+             ctypes.byref(kout), ctypes.byref(passes), stream_ptr())
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(centers.cpu().numpy(), ref_c)
+    np.testing.assert_array_equal(assign.cpu().numpy(), ref_a)
+
+
+def test_ranked_merge_of_a_snapshot_directory(ctx, tmp_path):
+    from tensor_adapt_b200.trainer import centroid_merge_ranked
+    vec, mass = o.cfg1_vectors(2, n_snap=8, per_snap=32)
+    d = tmp_path / "centroids"; d.mkdir()
+    for i, (v, m) in enumerate(zip(vec, mass)):
+        o.write_snapshot_file(str(d / f"step-{i:05d}.centroid"), v, float(m))
+    order = np.array([int(e.name[5:10]) for e in os.scandir(d) if e.name.endswith(".centroid")])
+    n, passes = centroid_merge_ranked(ctx, str(d), str(tmp_path / "bank.bin"), k=8, seed=5)
+    want_c, _, want_it, _, _ = o.kmeans_merge_ex(vec[order], mass[order], 8, 5)
+    assert n == len(vec) and passes == want_it
+    np.testing.assert_array_equal(o.read_merged_file(str(tmp_path / "bank.bin")), want_c)
