@@ -45,6 +45,17 @@ CONFIGS = {
 }
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel at the
+# three most frequent shapes of the qwen2-7b step, from one ncu capture of
+# `python -m tensor_adapt_b200.microbench gemm --M 16384 --N .. --K ..` (summary under profiles/), with the
+# launches of each shape per layer pass; `roofline.traffic` is their launch-weighted mean.
+NCU_GEMM_TRAFFIC_7B = {
+    "16384x18944x3584 (gate, up, dX of down)": (1.334e9, 3),
+    "16384x3584x18944 (down, halves of dX of gate+up)": (2.288e9, 3),
+    "16384x3584x3584 (q, o and their dX)": (0.369e9, 4),
+}
+
+
 def flops_per_token(mc, rank, targets, T):
     """Algorithmic FLOPs per trained token: frozen base forward + dX (no base dW), causal attention at
     half-square, LoRA without recompute."""
@@ -303,7 +314,11 @@ def main():
                     "h2d_bytes_per_step": 2 * 4 * b_local * T * world, "d2h_bytes_per_step": 16 * world},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "achieved": gemm_tf, "peak": peak, "unit": "TFLOP/s",
-                         "frac": (gemm_tf / peak) if gemm_tf else None, "traffic": None,
+                         "frac": (gemm_tf / peak) if gemm_tf else None,
+                         "traffic": (sum(b * n for b, n in NCU_GEMM_TRAFFIC_7B.values()) / sum(n for _, n in NCU_GEMM_TRAFFIC_7B.values())
+                                     if args.config == "qwen2-7b" else None),
+                         "traffic_note": ("bytes per launch, launch-weighted mean of ncu captures of the three dominant shapes; "
+                                          "algorithmic operand + output bytes of the same mix: 0.63e9" if args.config == "qwen2-7b" else None),
                          "peak_source": f"{src} bf16_tflops_sustained (kernel timed inside a long step)",
                          "kernel": "seg_gemm_kernel (tiles >= 128 wide)", "kernel_launches": int(nl[0]),
                          "kernel_ms_per_step": pm[0], "kernel_share_of_step": pm[0] / ms_dev,
