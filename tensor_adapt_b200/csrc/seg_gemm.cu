@@ -1,10 +1,11 @@
 // Segmented-K BF16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma with the
 // FP32 accumulator in TMEM -> tcgen05.ld epilogue (alpha, bias, residual, BF16/FP32 store).
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocator + MMA issuer (one elected lane)
-//   warps 2-5   epilogue: warp w owns TMEM lanes 32*(w%4) .. +31, i.e. 32 rows of the 128-row tile
+//   warps 2-9   epilogue: warp w owns TMEM lanes 32*(w%4) .. +31, i.e. 32 rows of a 128-row accumulator;
+//               the two warps of a lane group split the accumulators (256-row tiles) or the columns
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
 // main loop of tile i+1.  All waits are bounded (see ptx.cuh).
 #include "seg_gemm.h"
@@ -41,6 +42,7 @@ struct alignas(64) SegGemmParams {
 
 constexpr int BM = 128;       // rows of one MMA / one TMEM accumulator
 constexpr int BK = 64;
+constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, eight epilogue warps
 constexpr int GROUP_M = 16;   // m-tiles per raster group: a wave touches ~16 A tiles and ~9 B tiles -> L2 reuse
 
 constexpr uint32_t pow2_at_least(uint32_t v) { uint32_t p = 32; while (p < v) p <<= 1; return p; }
@@ -81,7 +83,7 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
 }
 
 template <int BN, int MH>
-__global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant__ SegGemmParams p) {
+__global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_constant__ SegGemmParams p) {
     using C = Cfg<BN, MH>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 4);
+            mbar_init(&tempty[b], 8);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -209,7 +211,11 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
             }
         }
     } else {
-        const int lg = warp & 3;   // TMEM lane group this warp may access
+        // Eight epilogue warps, two per TMEM lane group (a warp may only read lanes 32*(warp%4)..+31): with
+        // 256-row tiles one takes each accumulator, with 128-row tiles each takes half of the columns, so
+        // every scheduler has two warps to overlap TMEM reads with conversion and stores.
+        const int lg = warp & 3;
+        const int eh = (warp - 2) >> 2;
         uint32_t lt = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
             const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, BN);
@@ -218,13 +224,16 @@ __global__ void __launch_bounds__(192, 1) seg_gemm_kernel(const __grid_constant_
             if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
             tcgen05_fence_after_sync();
             constexpr int CW = BN >= 32 ? 32 : 16;
+            constexpr int NCH = BN / CW;
+            const int c_lo = MH == 2 ? 0 : eh * ((NCH + 1) / 2);
+            const int c_hi = MH == 2 ? NCH : (eh == 0 ? (NCH + 1) / 2 : NCH);
 #pragma unroll 1
-            for (int hh = 0; hh < MH; hh++) {
+            for (int hh = (MH == 2 ? eh : 0); hh < (MH == 2 ? eh + 1 : 1); hh++) {
                 const int row = tc.m0 + hh * BM + lg * 32 + lane;
                 const bool row_ok = row < p.M;
                 const uint32_t taddr = tmem_base + (MH == 2 ? uint32_t(hh) * 256u : buf * BN) + (uint32_t(lg * 32) << 16);
 #pragma unroll 1
-                for (int c = 0; c < BN / CW; c++) {
+                for (int c = c_lo; c < c_hi; c++) {
                     const int col0 = tc.n0 + c * CW;
                     if (col0 >= p.N) break;
                     float v[CW];
@@ -340,7 +349,7 @@ int launch(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int total_t
         attr_set[dev] = true;
     }
     const int grid = std::min(total_tiles, ctx->sm_count);
-    seg_gemm_kernel<BN, MH><<<grid, 192, Cfg<BN, MH>::SMEM, stream>>>(p);
+    seg_gemm_kernel<BN, MH><<<grid, kGemmThreads, Cfg<BN, MH>::SMEM, stream>>>(p);
     TA_LAUNCH_CHECK(ctx, "seg_gemm_kernel");
     return TA_OK;
 }
