@@ -77,6 +77,14 @@ int ta_rope(ta_ctx* ctx, void* q, int Hq, void* k, int Hk, int B, int T, int hea
 int ta_silu_mul_fwd(ta_ctx* ctx, const void* gate, const void* up, void* out, long n, void* stream);
 int ta_silu_mul_bwd(ta_ctx* ctx, const void* dout, const void* gate, const void* up, void* dgate, void* dup, long n,
                     void* stream);
+/* The head of Qwen2Base::forward + the loss + the head of Qwen2Base::backward in one call
+ * (src/base/arch/qwen2.cu:163-175 lm_head GEMM, src/backend/cuda/ops.cu:958-1020 cross_entropy_fwd,
+ * qwen2.cu:203-205 dres = dlogits.W): x [BT,H] BF16 (final-norm output), lm_head [V,H] BF16, targets
+ * [BT], loss [BT] FP32, dx [BT,H] BF16. Rows are processed chunk_rows at a time through
+ * logits_chunk [chunk_rows, V] BF16 (caller-provided device scratch), so no [BT,V] tensor exists;
+ * results are identical to running the three reference calls on the whole batch. */
+int ta_lmhead_ce_fwd_bwd(ta_ctx* ctx, const void* x, const void* lm_head, const int* targets, float* loss, void* dx, int BT, int H,
+                         int V, float inv_count, void* logits_chunk, int chunk_rows, void* stream);
 /* ops::cross_entropy_fwd (ops.hpp:90-96, ops.cu:958-1020). dlogits may be NULL (loss only) or alias
  * logits.  inv_count is the gradient scale: the reference uses 1/rows (ops.cu:1005); a micro-batched
  * or data-parallel step passes 1/(global token count). Targets < 0 behave as in the reference

@@ -54,6 +54,7 @@ _PROTOS = {
     "ta_silu_mul_fwd": (c_int, [P, P, P, P, c_long, P]),
     "ta_silu_mul_bwd": (c_int, [P, P, P, P, P, P, c_long, P]),
     "ta_cross_entropy_fwd": (c_int, [P, P, P, P, P, c_int, c_int, c_float, P]),
+    "ta_lmhead_ce_fwd_bwd": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, c_float, P, c_int, P]),
     "ta_embed_fwd": (c_int, [P, P, P, P, c_int, c_int, P]),
     "ta_add_bias": (c_int, [P, P, P, c_long, c_int, P]),
     "ta_add_inplace": (c_int, [P, P, P, c_long, P]),

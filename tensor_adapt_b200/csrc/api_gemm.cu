@@ -21,6 +21,26 @@ int ta_gemm_bf16(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, l
     return seg_gemm(ctx, static_cast<cudaStream_t>(stream), M, N, &s, 1, o);
 }
 
+// logits = x.W^T, loss / dlogits, dx = dlogits.W for `chunk_rows` rows at a time: the [BT, V] logits of the
+// reference (two 2.3 GiB tensors at 8 x 1024 tokens of a 152k vocabulary) shrink to one chunk buffer that
+// the cross-entropy kernel overwrites in place with the gradient.
+int ta_lmhead_ce_fwd_bwd(ta_ctx* ctx, const void* x, const void* lm_head, const int* targets, float* loss, void* dx, int BT, int H,
+                         int V, float inv_count, void* logits_chunk, int chunk_rows, void* stream) {
+    if (!ctx || !x || !lm_head || !targets || !loss || !dx || !logits_chunk || BT < 0 || H <= 0 || V <= 0 || chunk_rows <= 0)
+        return fail(ctx, TA_ERR_INVALID, "lmhead_ce_fwd_bwd: null argument or bad size");
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(dx);
+    for (int r0 = 0; r0 < BT; r0 += chunk_rows) {
+        const int rows = BT - r0 < chunk_rows ? BT - r0 : chunk_rows;
+        if (int rc = ta_gemm_bf16(ctx, rows, V, H, 1.f, xb + size_t(r0) * H, H, 0, lm_head, H, 0, nullptr, nullptr, logits_chunk, V, stream))
+            return rc;
+        if (int rc = ta_cross_entropy_fwd(ctx, logits_chunk, targets + r0, loss + r0, logits_chunk, rows, V, inv_count, stream)) return rc;
+        if (int rc = ta_gemm_bf16(ctx, rows, H, V, 1.f, logits_chunk, V, 0, lm_head, H, 1, nullptr, nullptr, dxb + size_t(r0) * H, H, stream))
+            return rc;
+    }
+    return TA_OK;
+}
+
 int ta_gemm_tokens_f32(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, long lda, const void* B, long ldb,
                        float* C, long ldc, int accumulate, int transpose_out, void* stream) {
     if (!ctx) return TA_ERR_INVALID;

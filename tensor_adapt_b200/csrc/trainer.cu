@@ -211,14 +211,8 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count) {
 
     // ── lm head + cross-entropy + head backward, in row chunks so [BT,V] never exists at once ──
     const bf16* lm = c.tie_embeddings ? t->embed : t->lm_head;
-    for (int r0 = 0; r0 < BT; r0 += t->logit_rows) {
-        const int rows = std::min(t->logit_rows, BT - r0);
-        RC(ta_gemm_bf16(ctx, rows, c.vocab, H, 1.f, t->x_final_normed + size_t(r0) * H, H, 0, lm, H, 0, nullptr, nullptr,
-                        t->logits, c.vocab, s));
-        RC(ta_cross_entropy_fwd(ctx, t->logits, t->tgt + r0, t->loss + r0, t->logits, rows, c.vocab, inv_count, s));
-        RC(ta_gemm_bf16(ctx, rows, H, c.vocab, 1.f, t->logits, c.vocab, 0, lm, H, 1, nullptr, nullptr,
-                        t->d_xn + size_t(r0) * H, H, s));
-    }
+    RC(ta_lmhead_ce_fwd_bwd(ctx, t->x_final_normed, lm, t->tgt, t->loss, t->d_xn, BT, H, c.vocab, inv_count, t->logits,
+                            t->logit_rows, s));
     loss_accum_kernel<<<1, 1024, 0, t->stream>>>(t->loss, BT, t->stats);
     TA_LAUNCH_CHECK(ctx, "loss_accum_kernel");
     // grad = rms_norm_bwd(dres, x_final, final_norm)                         (qwen2.cu:203-213)

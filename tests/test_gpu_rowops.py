@@ -136,3 +136,25 @@ def test_cross_entropy(ctx, rows, V):
     ctx.call("ta_cross_entropy_fwd", ptr(ld), ptr(td), ptr(loss), ptr(ld), rows, V, 1.0 / rows, stream_ptr())
     torch.cuda.synchronize()
     assert torch.equal(ld, dl)
+
+
+@pytest.mark.parametrize("BT,H,V,chunk", [(200, 128, 1000, 64), (96, 256, 4096, 96), (33, 64, 520, 1000)])
+def test_lmhead_ce_fwd_bwd_chunked(ctx, BT, H, V, chunk):
+    """lm head + cross-entropy + head backward through a chunk buffer equals the oracle's three
+    reference calls on the whole batch (ragged last chunk, chunk larger than the batch)."""
+    rng = np.random.default_rng(BT)
+    x = o.bf16_round(rng.standard_normal((BT, H), dtype=np.float32))
+    W = o.bf16_round(0.05 * rng.standard_normal((V, H), dtype=np.float32))
+    tgt = rng.integers(0, V, BT).astype(np.int32)
+    tgt[::7] = -1
+    logits = o.proj_fwd(W, x)
+    ref_loss, ref_d = o.cross_entropy_fwd(logits, tgt)
+    inv = 1.0 / 4096                                                     # a global-batch scale, not 1/BT
+    ref_dx = o.proj_bwd_x(W, o.bf16_round(ref_d * np.float32(BT * inv)))
+    xd, Wd, td = dev_bf16(x), dev_bf16(W), torch.from_numpy(tgt).cuda()
+    loss = torch.empty(BT, device="cuda"); dx = torch.empty_like(xd)
+    buf = torch.empty(min(chunk, BT) if chunk < BT else chunk, V, device="cuda", dtype=torch.bfloat16)
+    ctx.call("ta_lmhead_ce_fwd_bwd", ptr(xd), ptr(Wd), ptr(td), ptr(loss), ptr(dx), BT, H, V, inv, ptr(buf), chunk, stream_ptr())
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(loss.cpu().numpy(), ref_loss, rtol=3e-5, atol=3e-5)
+    assert np.abs(host(dx) - ref_dx).max() <= 2.0 ** -6 * np.abs(ref_dx).max() + 1e-9
