@@ -536,7 +536,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
     const int kv0 = kt * 128;
 
     if (threadIdx.x == 0) {
-        mbar_init(kv_full, 1); mbar_init(acc_full, 1); mbar_init(stat_full, 128);
+        mbar_init(kv_full, 1); mbar_init(acc_full, 1); mbar_init(stat_full, 2);
         for (int i = 0; i < QST; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
             mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
@@ -621,7 +621,10 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
             float* dlt = lse2 + 64;
             if (tid < 64) { lse2[tid] = next_l; dlt[tid] = next_d; }
             fetch(it + 1, next_l, next_d);
-            mbar_arrive(stat_full);   // all 64 entries of lse / delta are in shared memory after this phase
+            // the two warps that wrote the 64 entries of lse / delta publish them: one elected arrival each
+            // (an arrival per thread would be 128 serialised shared-memory atomics per sub-tile)
+            __syncwarp();
+            if (tid < 64 && lane == 0) mbar_arrive(stat_full);
             ATT_WAIT(stat_full, it & 1, DS_TIMEOUT_SOFTMAX);
             ATT_WAIT(&s_full[st], ph, DS_TIMEOUT_SOFTMAX);
             tcgen05_fence_after_sync();

@@ -87,6 +87,17 @@ int encode_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1,
 // Scratch of at least `bytes`, grown on demand when the context owns its workspace.
 int get_workspace(ta_ctx* ctx, size_t bytes, void** out);
 
+// Device allocation freed on scope exit (host-side helpers that return early on errors).
+struct DeviceBuffer {
+    void* p = nullptr;
+    DeviceBuffer() = default;
+    DeviceBuffer(const DeviceBuffer&) = delete;
+    DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+    ~DeviceBuffer() { if (p) cudaFree(p); }
+    cudaError_t alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 1); }
+    template <typename T> T* as() const { return static_cast<T*>(p); }
+};
+
 }  // namespace ta
 
 #define TA_CUDA(ctx, call)                                              \

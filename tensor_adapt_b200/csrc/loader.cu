@@ -498,10 +498,11 @@ int ta_trainer_load_base(ta_trainer* t, const char* dir, const char* arch_hint) 
         return fail(t->ctx, TA_ERR_INVALID, "config.json of " + std::string(dir) + " does not match the model config the trainer was created with");
     const long H = b.hidden, I = b.intermediate, V = b.vocab, qd = long(b.q_heads) * b.head_dim, kv = long(b.kv_heads) * b.head_dim;
     const long stage_elems = 8l << 20;   // 32 MB FP32 staging block, only touched for F32 checkpoints
-    float* stage = nullptr;
+    DeviceBuffer stage_buf;
     bool any_f32 = false;
     for (auto& kv2 : wf.entries) any_f32 |= kv2.second.dtype == 0;
-    if (any_f32) TA_CUDA(t->ctx, cudaMalloc(&stage, size_t(stage_elems) * 4));
+    if (any_f32) TA_CUDA(t->ctx, stage_buf.alloc(size_t(stage_elems) * 4));
+    float* stage = stage_buf.as<float>();
     int rc = upload_weight(t, wf, "model.embed_tokens.weight", t->embed, V * H, stage, stage_elems);
     for (int l = 0; l < b.layers && rc == TA_OK; l++) {
         const std::string p = "model.layers." + std::to_string(l) + ".";
@@ -522,7 +523,6 @@ int ta_trainer_load_base(ta_trainer* t, const char* dir, const char* arch_hint) 
     if (rc == TA_OK) rc = upload_weight(t, wf, "model.norm.weight", t->final_norm, H, stage, stage_elems);
     if (rc == TA_OK && !b.tie_embeddings) rc = upload_weight(t, wf, "lm_head.weight", t->lm_head, V * H, stage, stage_elems);
     cudaStreamSynchronize(t->stream);   // the shards are unmapped on return
-    if (stage) cudaFree(stage);
     if (rc) return rc;
     t->arch_name = bi.arch_name;
     t->base_sha = bi.sha;

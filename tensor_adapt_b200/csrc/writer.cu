@@ -228,32 +228,30 @@ static int merge_vectors(ta_ctx* ctx, const std::vector<std::vector<float>>& sna
     const int N = int(snaps.size());
     std::vector<float> flat(size_t(N) * D);
     for (int n = 0; n < N; n++) std::memcpy(flat.data() + size_t(n) * D, snaps[size_t(n)].data(), size_t(D) * 4);
-    float *dv = nullptr, *dc = nullptr;
-    int* da = nullptr;
     const int kk = std::min(k, N);
-    TA_CUDA(ctx, cudaMalloc(&dv, flat.size() * 4));
-    TA_CUDA(ctx, cudaMalloc(&dc, size_t(kk) * D * 4));
-    TA_CUDA(ctx, cudaMalloc(&da, size_t(N) * 4));
-    cudaMemcpy(dv, flat.data(), flat.size() * 4, cudaMemcpyHostToDevice);
+    DeviceBuffer bv, bc, ba, bm;
+    TA_CUDA(ctx, bv.alloc(flat.size() * 4));
+    TA_CUDA(ctx, bc.alloc(size_t(kk) * D * 4));
+    TA_CUDA(ctx, ba.alloc(size_t(N) * 4));
+    float *dv = bv.as<float>(), *dc = bc.as<float>();
+    int* da = ba.as<int>();
+    TA_CUDA(ctx, cudaMemcpy(dv, flat.data(), flat.size() * 4, cudaMemcpyHostToDevice));
     int kout = 0;
     int rc;
-    float* dm = nullptr;
     if (mo.extended) {
         if (mo.mass) {
-            TA_CUDA(ctx, cudaMalloc(&dm, size_t(N) * 4));
-            cudaMemcpy(dm, mo.mass->data(), size_t(N) * 4, cudaMemcpyHostToDevice);
+            TA_CUDA(ctx, bm.alloc(size_t(N) * 4));
+            TA_CUDA(ctx, cudaMemcpy(bm.p, mo.mass->data(), size_t(N) * 4, cudaMemcpyHostToDevice));
         }
-        rc = ta_kmeans_merge_ex(ctx, dv, dm, N, D, k, 50, mo.init_mode, mo.seed, mo.rank, dc, da, nullptr, nullptr, &kout, passes, nullptr);
+        rc = ta_kmeans_merge_ex(ctx, dv, bm.as<float>(), N, D, k, 50, mo.init_mode, mo.seed, mo.rank, dc, da, nullptr, nullptr, &kout,
+                                passes, nullptr);
     } else {
         rc = ta_kmeans_merge(ctx, dv, N, D, k, 50, dc, da, &kout, passes, nullptr);
     }
-    std::vector<float> centers(size_t(kk) * D);
-    if (rc == TA_OK) {
-        cudaStreamSynchronize(nullptr);
-        cudaMemcpy(centers.data(), dc, centers.size() * 4, cudaMemcpyDeviceToHost);
-    }
-    cudaFree(dv); cudaFree(dc); cudaFree(da); cudaFree(dm);
     if (rc) return rc;
+    std::vector<float> centers(size_t(kk) * D);
+    TA_CUDA(ctx, cudaStreamSynchronize(nullptr));
+    TA_CUDA(ctx, cudaMemcpy(centers.data(), dc, centers.size() * 4, cudaMemcpyDeviceToHost));
     std::ofstream f(out_path, std::ios::binary);
     if (!f) return fail(ctx, TA_ERR_IO, std::string("cannot write ") + out_path);
     f.write(reinterpret_cast<const char*>(&kout), 4);
