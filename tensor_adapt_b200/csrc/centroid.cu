@@ -110,22 +110,127 @@ __global__ void __launch_bounds__(kThreads) centroid_partial_kernel(const __nv_b
     }
 }
 
-__global__ void centroid_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ partial_w,
-                                       int nblocks, int D, int asbuilt, float* __restrict__ acc,
-                                       float* __restrict__ weight) {
-    const int d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d < D) {
-        float s = 0.f;
+// Warp-per-row variant for D <= 32*NV*8: a warp keeps its 1/32 slice of the accumulator in registers
+// (NV 16-byte vectors per lane), reads a row of g (norm) and the same row of h with every load of the row
+// in flight at once, and walks rows warp + k*warps-in-grid; the warps of a CTA are combined in warp order.
+template <int NV>
+__global__ void __launch_bounds__(kThreads) centroid_partial_warp_kernel(const __nv_bfloat16* __restrict__ h,
+                                                                         const __nv_bfloat16* __restrict__ g, int rows,
+                                                                         int pseudo_rows, int D, int asbuilt,
+                                                                         float* __restrict__ partial,
+                                                                         float* __restrict__ partial_w) {
+    constexpr int kWarps = kThreads / 32;
+    __shared__ float red[kWarps - 1][32 * 8 + 1];
+    __shared__ float wsum[kWarps];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nvec = D / 8, half_vec = nvec / 2;
+    float acc[NV][8];
+#pragma unroll
+    for (int j = 0; j < NV; j++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[j][e] = 0.f;
+    float wacc = 0.f;
+    for (int row = blockIdx.x * kWarps + warp; row < rows; row += gridDim.x * kWarps) {
+        const uint4* gr = reinterpret_cast<const uint4*>(g + size_t(row) * D);
+        const uint4* hr = reinterpret_cast<const uint4*>(h + size_t(row) * D);
+        uint4 gv[NV], hv[NV];
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = lane + 32 * j;
+            gv[j] = i < nvec ? gr[i] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = lane + 32 * j;
+            hv[j] = i < nvec ? hr[i] : make_uint4(0, 0, 0, 0);
+        }
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            float f[8];
+            unpack8c(gv[j], f);
+            float s = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; e++) s += f[e] * f[e];
+            if (asbuilt && lane + 32 * j >= half_vec) s1 += s; else s0 += s;
+        }
+        s0 = warp_sum(s0);
+        s1 = warp_sum(s1);
+        float g0, g1;
         if (!asbuilt) {
-            for (int b = 0; b < nblocks; b++) s += partial[size_t(b) * D + d];
-            acc[d] += s;
-        } else if (d & 1) {
-            const int m = d >> 1;
-            for (int b = 0; b < nblocks; b++) s += partial[size_t(b) * D + m] + partial[size_t(b) * D + D / 2 + m];
-            acc[d] += s;
+            g0 = g1 = sqrtf(s0);
+            wacc += g0;
+        } else {
+            g0 = (2 * row < pseudo_rows) ? sqrtf(s0) : 0.f;
+            g1 = (2 * row + 1 < pseudo_rows) ? sqrtf(s1) : 0.f;
+            wacc += g0 + g1;
+        }
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            float f[8];
+            unpack8c(hv[j], f);
+            const float gm = (asbuilt && lane + 32 * j >= half_vec) ? g1 : g0;
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[j][e] += f[e] * gm;
         }
     }
-    if (d == 0) {
+    // combine the CTA's warps in warp order, one vector slot at a time (bounded shared memory)
+    float* out = partial + size_t(blockIdx.x) * D;
+    if (lane == 0) wsum[warp] = wacc;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        __syncthreads();
+        if (warp > 0)
+#pragma unroll
+            for (int e = 0; e < 8; e++) red[warp - 1][lane * 8 + e] = acc[j][e];
+        __syncthreads();
+        if (warp == 0) {
+            const int i = lane + 32 * j;
+            float t[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                t[e] = acc[j][e];
+                for (int w = 0; w < kWarps - 1; w++) t[e] += red[w][lane * 8 + e];
+            }
+            if (i < nvec) {
+                *reinterpret_cast<float4*>(out + i * 8) = make_float4(t[0], t[1], t[2], t[3]);
+                *reinterpret_cast<float4*>(out + i * 8 + 4) = make_float4(t[4], t[5], t[6], t[7]);
+            }
+        }
+    }
+    if (threadIdx.x == 0) {
+        float w = 0.f;
+        for (int k = 0; k < kWarps; k++) w += wsum[k];
+        partial_w[blockIdx.x] = w;
+    }
+}
+
+// acc[d] += sum_b partial[b][d] in a fixed order: thread (x, y) sums blocks y, y+8, ... for column x, the
+// eight partial sums are then added in y order.
+__global__ void __launch_bounds__(256) centroid_reduce_kernel(const float* __restrict__ partial,
+                                                              const float* __restrict__ partial_w, int nblocks, int D,
+                                                              int asbuilt, float* __restrict__ acc,
+                                                              float* __restrict__ weight) {
+    __shared__ float part[8][33];
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+    const int d = blockIdx.x * 32 + x;          // source column (as-built: m of the first half)
+    const int ncol = asbuilt ? D / 2 : D;
+    float s = 0.f;
+    if (d < ncol) {
+        for (int b = y; b < nblocks; b += 8) {
+            const float* pr = partial + size_t(b) * D;
+            s += asbuilt ? pr[d] + pr[D / 2 + d] : pr[d];
+        }
+    }
+    part[y][x] = s;
+    __syncthreads();
+    if (y == 0 && d < ncol) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) t += part[k][x];
+        acc[asbuilt ? 2 * d + 1 : d] += t;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
         float w = 0.f;
         for (int b = 0; b < nblocks; b++) w += partial_w[b];
         *weight += w;
@@ -292,17 +397,24 @@ int ta_centroid_accumulate(ta_ctx* ctx, int mode, const void* hidden, const void
     if (BT == 0) return TA_OK;
     // as-built reads only the first BT*D BF16 elements of the FP32 buffers = tokens 0 .. ceil(BT/2)-1
     const int rows = asbuilt ? (BT + 1) / 2 : BT;
-    const int blocks = (rows + kRows - 1) / kRows;
+    const int nv = (D / 8 + 31) / 32;   // 16-byte vectors per lane in the warp-per-row kernel
+    const bool warp_rows = nv <= 16;
+    const int blocks = warp_rows ? std::min((rows + kThreads / 32 - 1) / (kThreads / 32), (nv <= 8 ? 2 : 1) * ctx->sm_count)
+                                 : (rows + kRows - 1) / kRows;
     void* ws = nullptr;
     if (int rc = get_workspace(ctx, size_t(blocks) * (D + 1) * sizeof(float), &ws)) return rc;
     float* partial = static_cast<float*>(ws);
     float* partial_w = partial + size_t(blocks) * D;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    centroid_partial_kernel<<<blocks, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(hidden),
-                                                        static_cast<const __nv_bfloat16*>(grad_signal), rows, BT, D,
-                                                        asbuilt, partial, partial_w);
+    const __nv_bfloat16* hb = static_cast<const __nv_bfloat16*>(hidden);
+    const __nv_bfloat16* gb = static_cast<const __nv_bfloat16*>(grad_signal);
+    if (!warp_rows) centroid_partial_kernel<<<blocks, kThreads, 0, s>>>(hb, gb, rows, BT, D, asbuilt, partial, partial_w);
+    else if (nv <= 4) centroid_partial_warp_kernel<4><<<blocks, kThreads, 0, s>>>(hb, gb, rows, BT, D, asbuilt, partial, partial_w);
+    else if (nv <= 8) centroid_partial_warp_kernel<8><<<blocks, kThreads, 0, s>>>(hb, gb, rows, BT, D, asbuilt, partial, partial_w);
+    else centroid_partial_warp_kernel<16><<<blocks, kThreads, 0, s>>>(hb, gb, rows, BT, D, asbuilt, partial, partial_w);
     TA_LAUNCH_CHECK(ctx, "centroid_partial_kernel");
-    centroid_reduce_kernel<<<(D + 255) / 256, 256, 0, s>>>(partial, partial_w, blocks, D, asbuilt, acc, weight);
+    const int ncol = asbuilt ? D / 2 : D;
+    centroid_reduce_kernel<<<(ncol + 31) / 32, 256, 0, s>>>(partial, partial_w, blocks, D, asbuilt, acc, weight);
     TA_LAUNCH_CHECK(ctx, "centroid_reduce_kernel");
     return TA_OK;
 }
