@@ -101,19 +101,26 @@ constexpr int kDqStages = 4;    // K/V ring of the dQ kernel (64-row tiles)
 constexpr int kDkvStages = 4;   // Q/dO ring of the dK/dV kernel (64-row tiles)
 
 // ─────────────────────────────── forward ───────────────────────────────
-// TMEM: S buffers at columns [0,128) and [128,256), O accumulator at [256, 256+HD).
+// Two independent softmax streams: key tiles of even index belong to warp group 0, odd ones to group 1.
+// Each group (four warps, one thread per query row) has its own score buffer, P buffer, running
+// (max, sum) and output accumulator, so the TMEM reads and the exponentials of one tile overlap with those
+// of the next and no group ever waits for the other; the two partial outputs are merged once at the end
+// (the split-KV identity O = (O0*2^(m0-M) + O1*2^(m1-M)) / (l0*2^(m0-M) + l1*2^(m1-M))).
+// TMEM: S of group g at columns [128g, 128g+128), O of group g at [256 + g*HD, 256 + (g+1)*HD).
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(320, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     constexpr uint32_t TB = Tile<HD>::BYTES;
-    constexpr int KS = 3;   // K ring: scores run two tiles ahead of the softmax, so three K tiles are live
-    constexpr uint32_t OFF_Q = 0, OFF_K = TB, OFF_V = (1 + KS) * TB, OFF_P = (3 + KS) * TB, OFF_BAR = (3 + KS) * TB + 32768;
+    constexpr int KS = 2;   // K ring (a slot is free again once its Q.K^T has completed, two tiles before it is needed)
+    constexpr uint32_t PB = 32768;   // one P tile [128 queries][128 keys] BF16; two of them, alternating by key tile
+    constexpr uint32_t OFF_Q = 0, OFF_K = TB, OFF_V = (1 + KS) * TB, OFF_P = (3 + KS) * TB, OFF_BAR = (3 + KS) * TB + 2 * PB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 4, *v_full = bars + 7, *v_empty = bars + 9,
-             *s_full = bars + 11, *s_empty = bars + 13, *p_full = bars + 15, *o_full = bars + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+             *s_full = bars + 11, *s_empty = bars + 13, *p_full = bars + 15, *o_full = bars + 17;
+    uint64_t* x_bar = bars + 19;   // one per TMEM lane group: the two warps that own the same rows meet here at the end
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,8 +139,9 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
         for (int i = 0; i < 2; i++) {
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+            mbar_init(&p_full[i], 4); mbar_init(&o_full[i], 1);
         }
-        mbar_init(p_full, 4); mbar_init(o_full, 1);
+        for (int i = 0; i < 4; i++) mbar_init(&x_bar[i], 2);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -148,15 +156,36 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
         if (lane == 0) {
             mbar_arrive_expect_tx(q_full, TB);
             load_tile<HD>(smem + OFF_Q, 16384, &p.tmQ, q_full, h * HD, b * p.T + q0);
-            for (int j = 0; j < n; j++) {
-                const int st = j & 1, kst = j % KS;
-                const uint32_t ph = (j >> 1) & 1;
-                ATT_WAIT(&k_empty[kst], ((j / KS) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
-                mbar_arrive_expect_tx(&k_full[kst], TB);
-                load_tile<HD>(smem + OFF_K + kst * TB, 16384, &p.tmK, &k_full[kst], hk * HD, b * p.T + j * 128);
-                ATT_WAIT(&v_empty[st], ph ^ 1u, DS_TIMEOUT_PRODUCER);
-                mbar_arrive_expect_tx(&v_full[st], TB);
-                load_tile<HD>(smem + OFF_V + st * TB, 16384, &p.tmV, &v_full[st], hk * HD, b * p.T + j * 128);
+            // K and V tiles are fetched by two independent cursors: a V slot only frees when the P.V two
+            // tiles back has completed, and the K tiles (needed two tiles ahead by the scores) must not queue
+            // behind that wait.
+            int jk = 0, jv = 0;
+            uint64_t t0 = 0;
+            for (uint32_t spin = 0; jk < n || jv < n; ++spin) {
+                bool progress = false;
+                if (jk < n && mbar_try_wait(&k_empty[jk % KS], ((jk / KS) & 1) ^ 1u)) {
+                    const int kst = jk % KS;
+                    mbar_arrive_expect_tx(&k_full[kst], TB);
+                    load_tile<HD>(smem + OFF_K + kst * TB, 16384, &p.tmK, &k_full[kst], hk * HD, b * p.T + jk * 128);
+                    jk++; progress = true;
+                }
+                if (jv < n && mbar_try_wait(&v_empty[jv & 1], ((jv >> 1) & 1) ^ 1u)) {
+                    const int st = jv & 1;
+                    mbar_arrive_expect_tx(&v_full[st], TB);
+                    load_tile<HD>(smem + OFF_V + st * TB, 16384, &p.tmV, &v_full[st], hk * HD, b * p.T + jv * 128);
+                    jv++; progress = true;
+                }
+                if (progress) { t0 = 0; continue; }
+                if ((spin & 63u) == 63u) {       // bounded like every other wait of the kernel
+                    if (*abort_flag) goto done;
+                    const uint64_t now = globaltimer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > WAIT_LIMIT_NS) {
+                        *abort_flag = 1;
+                        atomicCAS(p.status, 0, int(DS_TIMEOUT_PRODUCER));
+                        goto done;
+                    }
+                }
             }
         }
     } else if (warp == 1) {
@@ -179,35 +208,36 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
                 if (j >= 0) {      // O += P_j . V_j once the softmax warps have published P_j (and rescaled O)
                     const int st = j & 1;
                     ATT_WAIT(&v_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
-                    ATT_WAIT(p_full, j & 1, DS_TIMEOUT_MMA);
+                    ATT_WAIT(&p_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
                     tcgen05_fence_after_sync();
-                    mma_kmn<HD, 128>(TM_O, dPd, dVd + ((st * TB) >> 4), j > 0);
+                    mma_kmn<HD, 128>(TM_O + st * HD, dPd + ((st * PB) >> 4), dVd + ((st * TB) >> 4), j > 1);
                     umma_commit(&v_empty[st]);
-                    umma_commit(o_full);
+                    umma_commit(&o_full[st]);
                 }
             }
         }
     } else {
-        const int lg = warp & 3;
+        const int lg = warp & 3, grp = (warp - 2) >> 2;   // grp: 0 = even key tiles, 1 = odd key tiles
         const int row = lg * 32 + lane;
         const int q_idx = q0 + row;
         const uint32_t lane_addr = uint32_t(lg * 32) << 16;
+        const uint32_t TM_OG = TM_O + grp * HD;
         float m = -INFINITY, l = 0.f;
-        uint8_t* sP = smem + OFF_P;
+        uint8_t* sP = smem + OFF_P + grp * PB;
 
-        for (int j = 0; j < n; j++) {
-            const int st = j & 1;
-            ATT_WAIT(&s_full[st], (j >> 1) & 1, DS_TIMEOUT_SOFTMAX);
+        for (int j = grp; j < n; j += 2) {
+            const uint32_t ph = (j >> 1) & 1;
+            ATT_WAIT(&s_full[grp], ph, DS_TIMEOUT_SOFTMAX);
             tcgen05_fence_after_sync();
             const bool diag = (j == qt);
-            const uint32_t ts = tmem + st * 128 + lane_addr;
+            const uint32_t ts = tmem + grp * 128 + lane_addr;
             uint32_t s[4][32];
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_ld_x32(ts + c * 32, s[c]);
             tmem_ld_wait();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[st]);   // the scores are in registers: S buffer is free
+            if (lane == 0) mbar_arrive(&s_empty[grp]);   // the scores are in registers: S buffer is free
             float mx = -INFINITY;
 #pragma unroll
             for (int c = 0; c < 4; c++)
@@ -220,46 +250,36 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
                 }
             float alpha = 1.f;
             bool rescale = false;
-            if (j == 0) {
+            if (j < 2) {
                 m = mx;
             } else if (mx > m + kRescaleThreshold) {
                 alpha = ex2_approx(m - mx);
                 m = mx;
                 rescale = true;
             }
-            // Three separate passes so that the 128 special-function ops are issued back to back: with one
-            // softmax warp per scheduler there is no other warp to hide the MUFU latency behind.
-#pragma unroll
-            for (int c = 0; c < 4; c++)
-#pragma unroll
-                for (int i = 0; i < 32; i++) s[c][i] = __float_as_uint(__uint_as_float(s[c][i]) - m);
-#pragma unroll
-            for (int c = 0; c < 4; c++)
-#pragma unroll
-                for (int i = 0; i < 32; i++) s[c][i] = __float_as_uint(ex2_approx(__uint_as_float(s[c][i])));
             uint32_t pk[64];
             float sum = 0.f;
 #pragma unroll
             for (int c = 0; c < 4; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = __uint_as_float(s[c][i]), p1 = __uint_as_float(s[c][i + 1]);
+                    const float p0 = ex2_approx(__uint_as_float(s[c][i]) - m), p1 = ex2_approx(__uint_as_float(s[c][i + 1]) - m);
                     sum += p0 + p1;
                     pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
                 }
-            if (j > 0) {
-                // P buffer and O are only safe to touch once the previous P.V has completed
-                ATT_WAIT(o_full, (j - 1) & 1, DS_TIMEOUT_SOFTMAX);
+            if (j >= 2) {
+                // this group's P buffer and accumulator were last used by P.V of its previous tile (j-2)
+                ATT_WAIT(&o_full[grp], ph ^ 1u, DS_TIMEOUT_SOFTMAX);
                 tcgen05_fence_after_sync();
                 if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
                     for (int c = 0; c < HD / 32; c++) {
                         uint32_t r[32];
-                        tmem_ld_x32(TM_O + lane_addr + c * 32, r);
+                        tmem_ld_x32(TM_OG + lane_addr + c * 32, r);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st_x32(TM_O + lane_addr + c * 32, r);
+                        tmem_st_x32(TM_OG + lane_addr + c * 32, r);
                     }
                     tmem_st_wait();
                 }
@@ -272,30 +292,54 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_kernel(const __grid_constant_
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(&p_full[grp]);
         }
-        ATT_WAIT(o_full, (n - 1) & 1, DS_TIMEOUT_SOFTMAX);
+        // last P.V of this group, then the two groups exchange (max, sum) per row through their idle P buffers
+        const int cnt = (n - grp + 1) / 2;   // key tiles this group processed
+        if (cnt > 0) {
+            ATT_WAIT(&o_full[grp], (cnt - 1) & 1, DS_TIMEOUT_SOFTMAX);
+            tcgen05_fence_after_sync();
+        }
+        float2* mine = reinterpret_cast<float2*>(sP);
+        const float2* other = reinterpret_cast<const float2*>(smem + OFF_P + (grp ^ 1) * PB);
+        mine[row] = make_float2(m, l);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&x_bar[lg]);
+        ATT_WAIT(&x_bar[lg], 0, DS_TIMEOUT_SOFTMAX);   // both groups have seen their last P.V complete
         tcgen05_fence_after_sync();
-        const float inv_l = 1.f / l;
+        const float2 o = other[row];
+        const bool both = n > 1;                 // with a single key tile group 1 never ran: its accumulator is undefined
+        const float m0 = grp == 0 ? m : o.x, l0 = grp == 0 ? l : o.y;
+        const float m1 = grp == 0 ? o.x : m, l1 = grp == 0 ? o.y : l;
+        const float M = both ? fmaxf(m0, m1) : m0;
+        const float w0 = ex2_approx(m0 - M), w1 = both ? ex2_approx(m1 - M) : 0.f;
+        const float L = l0 * w0 + l1 * w1;
+        const float f0 = w0 / L, f1 = w1 / L;
         const bool ok = q_idx < p.T;
         __nv_bfloat16* orow = p.out + (size_t(b) * p.T + q_idx) * (size_t(p.Hq) * HD) + h * HD;
+        // each group normalises and stores half of the head dimension
 #pragma unroll
-        for (int c = 0; c < HD / 32; c++) {
-            uint32_t r[32];
-            tmem_ld_x32(TM_O + lane_addr + c * 32, r);
+        for (int c = grp * (HD / 64); c < (grp + 1) * (HD / 64); c++) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_x32(TM_O + lane_addr + c * 32, r0);
+            if (both) tmem_ld_x32(TM_O + HD + lane_addr + c * 32, r1);
             tmem_ld_wait();
             if (ok) {
 #pragma unroll
                 for (int g = 0; g < 4; g++) {
                     uint32_t w[4];
 #pragma unroll
-                    for (int i = 0; i < 4; i++)
-                        w[i] = pack_bf16x2(__uint_as_float(r[g * 8 + i * 2]) * inv_l, __uint_as_float(r[g * 8 + i * 2 + 1]) * inv_l);
+                    for (int i = 0; i < 4; i++) {
+                        const int e = g * 8 + i * 2;
+                        float a0 = __uint_as_float(r0[e]) * f0, a1 = __uint_as_float(r0[e + 1]) * f0;
+                        if (both) { a0 += __uint_as_float(r1[e]) * f1; a1 += __uint_as_float(r1[e + 1]) * f1; }
+                        w[i] = pack_bf16x2(a0, a1);
+                    }
                     *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
         }
-        if (ok) p.lse[(size_t(b) * p.Hq + h) * p.T + q_idx] = m * kLn2 + logf(l);
+        if (ok && grp == 0) p.lse[(size_t(b) * p.Hq + h) * p.T + q_idx] = M * kLn2 + logf(L);
     }
 done:
     __syncwarp();
@@ -711,7 +755,7 @@ done:
     if (warp == 1) { tcgen05_fence_after_sync(); tmem_dealloc(tmem, 512); }
 }
 
-template <int HD> constexpr size_t fwd_smem() { return 6 * Tile<HD>::BYTES + 32768 + 256 + 1024; }
+template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 2 * 32768 + 256 + 1024; }
 template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 2 * kDqStages * Tile<HD>::BYTES64 + 32768 + 256 + 1024; }
 template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 32768 + 1024 + 256 + 1024; }
 
@@ -767,10 +811,10 @@ int ta_flash_attn_fwd(ta_ctx* ctx, const void* Q, const void* K, const void* V, 
     ProfScope prof(ctx, s, PROF_ATTN_FWD, 2.0 * 2.0 * B * Hq * double(T) * T * head_dim * 0.5);
     if (head_dim == 128) {
         if (int rc = set_smem(ctx, attn_fwd_kernel<128>, fwd_smem<128>())) return rc;
-        attn_fwd_kernel<128><<<grid, 192, fwd_smem<128>(), s>>>(p);
+        attn_fwd_kernel<128><<<grid, 320, fwd_smem<128>(), s>>>(p);
     } else {
         if (int rc = set_smem(ctx, attn_fwd_kernel<64>, fwd_smem<64>())) return rc;
-        attn_fwd_kernel<64><<<grid, 192, fwd_smem<64>(), s>>>(p);
+        attn_fwd_kernel<64><<<grid, 320, fwd_smem<64>(), s>>>(p);
     }
     TA_LAUNCH_CHECK(ctx, "attn_fwd_kernel");
     return TA_OK;
