@@ -123,6 +123,10 @@ __global__ void __launch_bounds__(320, 1) attn_fwd_kernel(const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+    if (blockDim.x != 320) {   // the warp roles below assume ten warps: refuse any other launch shape
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, int(DS_BAD_LAUNCH));
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // 1-D grid ordered heavy-first over the WHOLE launch: late query tiles (most key tiles) of every
     // (head, batch) come before any lighter tile

@@ -145,7 +145,8 @@ int ta_device_status(ta_ctx* ctx, int* status) {
     if (!ctx || !status) return TA_ERR_INVALID;
     TA_CUDA(ctx, cudaMemcpy(status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (*status != 0) {
-        ctx->last_error = "a bounded device wait ran out (status " + std::to_string(*status) + ")";
+        ctx->last_error = *status == 105 ? std::string("a kernel refused its launch shape (status 105)")
+                                         : "a bounded device wait ran out (status " + std::to_string(*status) + ")";
         cudaMemset(ctx->d_status, 0, sizeof(int));
         return TA_ERR_DEVICE_TIMEOUT;
     }

@@ -20,6 +20,7 @@ enum DeviceStatus : int {
     DS_TIMEOUT_MMA      = 102,   // MMA issuer waited too long for data / a free accumulator
     DS_TIMEOUT_EPILOGUE = 103,   // epilogue waited too long for an accumulator
     DS_TIMEOUT_SOFTMAX  = 104,   // attention softmax warps waited too long
+    DS_BAD_LAUNCH       = 105,   // a kernel was launched with a block size its warp roles do not match
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
