@@ -82,6 +82,84 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
     return t;
 }
 
+// Drains columns [c_lo*CW, c_hi*CW) of one 128-row accumulator: TMEM -> registers -> alpha, bias, residual
+// -> BF16 / FP32 store (or split-K partial).  `row` is the global output row of this thread's TMEM lane.
+template <int CW>
+__device__ __forceinline__ void epilogue_chunks(const SegGemmParams& p, uint32_t taddr, int row, bool row_ok, int n0,
+                                                int split, int c_lo, int c_hi) {
+#pragma unroll 1
+    for (int c = c_lo; c < c_hi; c++) {
+        const int col0 = n0 + c * CW;
+        if (col0 >= p.N) break;
+        float v[CW];
+        if constexpr (CW == 32) {
+            uint32_t r[32];
+            tmem_ld_x32(taddr + c * CW, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+        } else {
+            uint32_t r[16];
+            tmem_ld_x16(taddr + c * CW, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+        }
+        if (!row_ok) continue;
+#pragma unroll
+        for (int g = 0; g < CW / 8; g++) {
+            const int col = col0 + g * 8;
+            if (col >= p.N) break;
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] = v[g * 8 + i] * p.alpha;
+            if (p.bias) {
+                const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = unpack_bf16x2(bw[i]);
+                    o[2 * i] += f.x;
+                    o[2 * i + 1] += f.y;
+                }
+            }
+            if (p.f32) {
+                float* dst = p.ws
+                                 ? p.ws + size_t(split) * p.ws_split_stride + size_t(row) * p.N + col
+                                 : reinterpret_cast<float*>(p.C) + size_t(row) * p.ldc + col;
+                float4 lo = make_float4(o[0], o[1], o[2], o[3]);
+                float4 hi = make_float4(o[4], o[5], o[6], o[7]);
+                if (p.accumulate && !p.ws) {
+                    const float4 a = *reinterpret_cast<const float4*>(dst);
+                    const float4 b = *reinterpret_cast<const float4*>(dst + 4);
+                    lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+                    hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+                }
+                *reinterpret_cast<float4*>(dst) = lo;
+                *reinterpret_cast<float4*>(dst + 4) = hi;
+            } else {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col;
+                if (p.residual) {
+                    const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldc + col);
+                    const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f = unpack_bf16x2(rw[i]);
+                        o[2 * i] += f.x;
+                        o[2 * i + 1] += f.y;
+                    }
+                }
+                uint4 w;
+                w.x = pack_bf16x2(o[0], o[1]);
+                w.y = pack_bf16x2(o[2], o[3]);
+                w.z = pack_bf16x2(o[4], o[5]);
+                w.w = pack_bf16x2(o[6], o[7]);
+                *reinterpret_cast<uint4*>(dst) = w;
+            }
+        }
+    }
+}
+
 template <int BN, int MH>
 __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_constant__ SegGemmParams p) {
     using C = Cfg<BN, MH>;
@@ -232,77 +310,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
                 const int row = tc.m0 + hh * BM + lg * 32 + lane;
                 const bool row_ok = row < p.M;
                 const uint32_t taddr = tmem_base + (MH == 2 ? uint32_t(hh) * 256u : buf * BN) + (uint32_t(lg * 32) << 16);
-#pragma unroll 1
-                for (int c = c_lo; c < c_hi; c++) {
-                    const int col0 = tc.n0 + c * CW;
-                    if (col0 >= p.N) break;
-                    float v[CW];
-                    if constexpr (CW == 32) {
-                        uint32_t r[32];
-                        tmem_ld_x32(taddr + c * CW, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
-                    } else {
-                        uint32_t r[16];
-                        tmem_ld_x16(taddr + c * CW, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-                    }
-                    if (!row_ok) continue;
-#pragma unroll
-                    for (int g = 0; g < CW / 8; g++) {
-                        const int col = col0 + g * 8;
-                        if (col >= p.N) break;
-                        float o[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) o[i] = v[g * 8 + i] * p.alpha;
-                        if (p.bias) {
-                            const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
-                            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                const float2 f = unpack_bf16x2(bw[i]);
-                                o[2 * i] += f.x;
-                                o[2 * i + 1] += f.y;
-                            }
-                        }
-                        if (p.f32) {
-                            float* dst = p.ws
-                                             ? p.ws + size_t(tc.split) * p.ws_split_stride + size_t(row) * p.N + col
-                                             : reinterpret_cast<float*>(p.C) + size_t(row) * p.ldc + col;
-                            float4 lo = make_float4(o[0], o[1], o[2], o[3]);
-                            float4 hi = make_float4(o[4], o[5], o[6], o[7]);
-                            if (p.accumulate && !p.ws) {
-                                const float4 a = *reinterpret_cast<const float4*>(dst);
-                                const float4 b = *reinterpret_cast<const float4*>(dst + 4);
-                                lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
-                                hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
-                            }
-                            *reinterpret_cast<float4*>(dst) = lo;
-                            *reinterpret_cast<float4*>(dst + 4) = hi;
-                        } else {
-                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col;
-                            if (p.residual) {
-                                const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldc + col);
-                                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-                                for (int i = 0; i < 4; i++) {
-                                    const float2 f = unpack_bf16x2(rw[i]);
-                                    o[2 * i] += f.x;
-                                    o[2 * i + 1] += f.y;
-                                }
-                            }
-                            uint4 w;
-                            w.x = pack_bf16x2(o[0], o[1]);
-                            w.y = pack_bf16x2(o[2], o[3]);
-                            w.z = pack_bf16x2(o[4], o[5]);
-                            w.w = pack_bf16x2(o[6], o[7]);
-                            *reinterpret_cast<uint4*>(dst) = w;
-                        }
-                    }
-                }
+                epilogue_chunks<CW>(p, taddr, row, row_ok, tc.n0, tc.split, c_lo, c_hi);
             }
             tcgen05_fence_before_sync();
             __syncwarp();
@@ -321,6 +329,170 @@ done:
     if (warp == 1) {
         tcgen05_fence_after_sync();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ── CTA-pair kernel ─────────────────────────────────────────────────────────
+// Two CTAs (a cluster of two, on neighbouring SMs) work on one 512 x BN tile: each owns 256 rows (two
+// accumulators, all 512 TMEM columns) and HALF of every B tile.  One thread of the rank-0 CTA issues
+// tcgen05.mma.cta_group::2 instructions (M = 256: 128 rows from each CTA's shared memory, N = BN: the two
+// halves of B from the two CTAs), so per FLOP each SM fills and reads a third less shared memory than the
+// single-CTA 256-row kernel.  K-major A only; B K-major or MN-major; no split-K.
+//
+// Barriers: full[s] lives in rank 0 (both producers announce their bytes there, both CTAs' loads complete
+// on it); empty[s] and tfull live in each CTA (rank 0 commits to both); tempty lives in rank 0 (the epilogue
+// warps of both CTAs arrive there).  Every wait is bounded; the cluster barrier at the end keeps either
+// CTA's shared memory alive until its peer is done with it.
+template <int BN>
+struct PairCfg {
+    static constexpr int STAGES = 4;
+    static constexpr uint32_t A_BYTES = 256 * BK * 2;
+    static constexpr uint32_t B_BYTES = 128 * BK * 2;              // half tile (BN/2 <= 128 rows, or two 64-column chunks)
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    seg_gemm_pair_kernel(const __grid_constant__ SegGemmParams p) {
+    using C = PairCfg<BN>;
+    constexpr int HALF = BN / 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* tfull = empty + C::STAGES;
+    uint64_t* tempty = tfull + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(&full[s], 2);      // one arrive.expect_tx from each CTA's producer
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tfull, 1);
+        mbar_init(tempty, 16);           // eight epilogue warps in each CTA
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                  // the peer's barriers are initialised before anything arrives on them
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int m_tiles = (p.M + 511) / 512;
+    const int n_tiles = (p.N + BN - 1) / BN;
+    const int total = m_tiles * n_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int s = 0; s < p.nseg; s++) {
+                prefetch_tensormap(&p.tmA[s]);
+                prefetch_tensormap(&p.tmB[s]);
+            }
+            uint32_t it = 0;
+            for (int tile = pair; tile < total; tile += npairs) {
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 512, BN);
+                const int m0 = tc.m0 + int(rank) * 256, nh = tc.n0 + int(rank) * HALF;
+                for (int s = 0; s < p.nseg; s++) {
+                    const int nkb = (p.K[s] + BK - 1) / BK;
+                    const bool b_mn = p.b_mn[s] != 0;
+                    for (int kb = 0; kb < nkb; kb++, it++) {
+                        const uint32_t stage = it % C::STAGES;
+                        const uint32_t ph = (it / C::STAGES) & 1u;
+                        if (!mbar_wait(&empty[stage], ph ^ 1u, abort_flag, p.status, DS_TIMEOUT_PRODUCER)) goto done;
+                        uint8_t* sa = smem + stage * C::STAGE_BYTES;
+                        uint8_t* sb = sa + C::A_BYTES;
+                        const uint32_t fbar = map_to_cta(smem_u32(&full[stage]), 0);
+                        mbar_arrive_expect_tx_cluster(fbar, C::STAGE_BYTES);
+                        tma_load_2d_pair(sa, &p.tmA[s], fbar, kb * BK, m0);             // box {64, 256}
+                        if (!b_mn) {
+                            tma_load_2d_pair(sb, &p.tmB[s], fbar, kb * BK, nh);         // box {64, 128}
+                        } else {
+                            tma_load_2d_pair(sb, &p.tmB[s], fbar, nh, kb * BK);         // box {64, 64} x 2
+                            tma_load_2d_pair(sb + 8192, &p.tmB[s], fbar, nh + 64, kb * BK);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t peer_empty0 = map_to_cta(smem_u32(&empty[0]), 1), peer_tfull = map_to_cta(smem_u32(tfull), 1);
+            uint32_t it = 0, lt = 0;
+            for (int tile = pair; tile < total; tile += npairs, lt++) {
+                if (!mbar_wait(tempty, (lt & 1u) ^ 1u, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
+                tcgen05_fence_after_sync();
+                uint32_t acc = 0;
+                for (int s = 0; s < p.nseg; s++) {
+                    const int nkb = (p.K[s] + BK - 1) / BK;
+                    const bool b_mn = p.b_mn[s] != 0;
+                    const uint32_t idesc = umma_idesc_bf16(256, BN, false, b_mn);
+                    for (int kb = 0; kb < nkb; kb++, it++) {
+                        const uint32_t stage = it % C::STAGES;
+                        const uint32_t ph = (it / C::STAGES) & 1u;
+                        if (!mbar_wait(&full[stage], ph, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
+                        tcgen05_fence_after_sync();
+                        const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                        const uint32_t sb = sa + C::A_BYTES;
+                        const int krem = p.K[s] - kb * BK;
+                        const int kinstr = krem >= BK ? 4 : (krem + 15) / 16;
+                        for (int ki = 0; ki < kinstr; ki++) {
+                            const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
+                                                     : smem_desc_sw128(sb + ki * 32, 16, 1024);
+#pragma unroll
+                            for (int hh = 0; hh < 2; hh++)
+                                umma_bf16_pair(tmem_base + hh * 256, smem_desc_sw128(sa + hh * 16384 + ki * 32, 16, 1024), bd, idesc, acc);
+                            acc = 1;
+                        }
+                        umma_commit_pair(smem_u32(&empty[stage]));
+                        umma_commit_pair(peer_empty0 + stage * 8);
+                    }
+                }
+                umma_commit_pair(smem_u32(tfull));
+                umma_commit_pair(peer_tfull);
+            }
+        }
+    } else {
+        const int lg = warp & 3;
+        const int eh = (warp - 2) >> 2;
+        const uint32_t tempty0 = map_to_cta(smem_u32(tempty), 0);
+        uint32_t lt = 0;
+        for (int tile = pair; tile < total; tile += npairs, lt++) {
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 512, BN);
+            if (!mbar_wait(tfull, lt & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
+            tcgen05_fence_after_sync();
+            const int row = tc.m0 + int(rank) * 256 + eh * BM + lg * 32 + lane;
+            const uint32_t taddr = tmem_base + uint32_t(eh) * 256u + (uint32_t(lg * 32) << 16);
+            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, 0, BN / 32);
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0);
+        }
+    }
+
+done:
+    __syncwarp();
+    if (*abort_flag) {
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                  // neither CTA leaves while the other may still signal or read it
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -351,6 +523,21 @@ int launch(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int total_t
     const int grid = std::min(total_tiles, ctx->sm_count);
     seg_gemm_kernel<BN, MH><<<grid, kGemmThreads, Cfg<BN, MH>::SMEM, stream>>>(p);
     TA_LAUNCH_CHECK(ctx, "seg_gemm_kernel");
+    return TA_OK;
+}
+
+template <int BN>
+int launch_pair(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int total_pair_tiles) {
+    static bool attr_set[64] = {};
+    const int dev = ctx->device & 63;
+    if (!attr_set[dev]) {
+        TA_CUDA(ctx, cudaFuncSetAttribute(seg_gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          int(PairCfg<BN>::SMEM)));
+        attr_set[dev] = true;
+    }
+    const int grid = 2 * std::min(total_pair_tiles, ctx->sm_count / 2);
+    seg_gemm_pair_kernel<BN><<<grid, kGemmThreads, PairCfg<BN>::SMEM, stream>>>(p);
+    TA_LAUNCH_CHECK(ctx, "seg_gemm_pair_kernel");
     return TA_OK;
 }
 
@@ -441,6 +628,11 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     for (int s = 0; s < nseg; s++) { ksum_all += segs[s].K; any_a_mn = any_a_mn || segs[s].a_mn; }
     const TileChoice tcfg = out.split_k > 1 ? TileChoice{pick_bn(N), 1} : pick_tile(M, N, ksum_all, any_a_mn, ctx->sm_count);
     const int bn = tcfg.bn, tile_m = 128 * tcfg.mh;
+    // CTA-pair kernel (512 x 256 tiles over two SMs): same A boxes as the 256-row kernel, half-width B boxes.
+    // Opt-in (TA_GEMM_PAIR=1): measured 3-7 % slower than the single-CTA 256-row kernel on the 7B shapes.
+    const char* pair_env = std::getenv("TA_GEMM_PAIR");
+    const bool pair_enabled = pair_env && pair_env[0] == '1';
+    const bool use_pair = pair_enabled && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
     SegGemmParams p;
     std::memset(&p, 0, sizeof(p));
     for (int s = 0; s < nseg; s++) {
@@ -455,7 +647,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
         if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, uint32_t(tile_m), &p.tmA[s]);
         else         rc = get_tmap_bf16(ctx, g.A, uint64_t(M), uint64_t(g.K), uint64_t(g.lda) * 2, 64, 64, &p.tmA[s]);
         if (rc) return rc;
-        if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(bn), &p.tmB[s]);
+        if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(use_pair ? bn / 2 : bn), &p.tmB[s]);
         else         rc = get_tmap_bf16(ctx, g.B, uint64_t(N), uint64_t(g.K), uint64_t(g.ldb) * 2, 64, 64, &p.tmB[s]);
         if (rc) return rc;
         p.K[s] = g.K;
@@ -489,7 +681,9 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     for (int s = 0; s < nseg; s++) ksum += segs[s].K;
     ProfScope prof(out.no_host_state ? nullptr : ctx, stream, bn >= 128 ? PROF_GEMM : PROF_GEMM_SKINNY, 2.0 * M * N * ksum);
     int rc;
-    if (tcfg.mh == 2) {
+    if (use_pair) {
+        rc = launch_pair<256>(ctx, stream, p, ((M + 511) / 512) * n_tiles);
+    } else if (tcfg.mh == 2) {
         rc = bn == 224 ? launch<224, 2>(ctx, stream, p, total) : launch<256, 2>(ctx, stream, p, total);
     } else {
         switch (bn) {
