@@ -84,6 +84,18 @@ __device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint64_t a_desc, uint64
                   (accumulate || ks) ? 1u : 0u);
 }
 
+// D[128, HD] (+)= A[128, KT] . B[KT (k), HD (n)] with A read from TENSOR MEMORY: BF16 packed two per
+// 32-bit column (column c of the lane holds k = 2c and 2c+1), so a K = 16 step advances eight columns;
+// B as in mma_kmn.  Halves the shared-memory operand traffic of the contraction and needs no P / dS tile
+// in shared memory at all.
+template <int HD, int KT>
+__device__ __forceinline__ void mma_tmn(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, bool accumulate) {
+    constexpr uint32_t idesc = umma_idesc_bf16(128, HD, false, true);
+#pragma unroll
+    for (int ks = 0; ks < KT / 16; ks++)
+        umma_bf16_ts(d_tmem, a_tmem + ks * 8, b_desc + ((ks * 2048) >> 4), idesc, (accumulate || ks) ? 1u : 0u);
+}
+
 template <int HD>
 __device__ __forceinline__ void load_tile(uint8_t* dst, uint32_t chunk_bytes, const CUtensorMap* tm, uint64_t* bar,
                                           int col0, int row0) {
@@ -557,19 +569,23 @@ done:
 // ─────────────────────────────── backward: dK, dV ───────────────────────────────
 // CTA = 128 key rows of one KV head; queries are walked in sub-tiles of 64 rows over all query heads of
 // the group.  TMEM: S^T[2] at [0,128), dP^T[2] at [128,256), dV at [256,256+HD), dK at [256+HD,256+2HD).
+// P^T and dS^T never touch shared memory: each element-wise thread overwrites the first 32 columns of its
+// S^T / dP^T row with the BF16 pairs, and dV += P^T.dO, dK += dS^T.Q read that A operand from TMEM.  The
+// tensor pipe executes in issue order, so S^T of sub-tile it+2 (issued after dV/dK of sub-tile it) cannot
+// overwrite a P^T that is still being read.
 
 template <int HD>
 __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
     constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
     constexpr int QST = kDkvStages;   // Q/dO ring depth (a stage is released only after dV, dK consumed it)
-    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + QST * TB64, OFF_PT = 2 * TB + 2 * QST * TB64,
-                       OFF_DST = OFF_PT + 16384, OFF_STAT = OFF_DST + 16384, OFF_BAR = OFF_STAT + 1024;
+    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + QST * TB64, OFF_STAT = 2 * TB + 2 * QST * TB64,
+                       OFF_BAR = OFF_STAT + 1024;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 1 + QST, *s_full = bars + 1 + 2 * QST,
-             *s_empty = s_full + 2, *p_full = s_full + 4, *p_empty = s_full + 6, *acc_full = s_full + 8, *stat_full = s_full + 9;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 10);
+             *p_full = s_full + 2, *acc_full = s_full + 4, *stat_full = s_full + 5;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* stat = reinterpret_cast<float*>(smem + OFF_STAT);   // [2 buffers][lse2 64 | delta 64]
 
@@ -587,9 +603,8 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
         mbar_init(kv_full, 1); mbar_init(acc_full, 1); mbar_init(stat_full, 2);
         for (int i = 0; i < QST; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
-            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+            mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4);
         }
-        mbar_init(p_full, 4); mbar_init(p_empty, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -617,28 +632,27 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
         if (lane == 0) {
             const uint64_t dKd = desc_k(smem_u32(smem + OFF_K)), dVd = desc_k(smem_u32(smem + OFF_V)),
                            dQk = desc_k(smem_u32(smem + OFF_Q)), dDOk = desc_k(smem_u32(smem + OFF_DO)),
-                           dQmn = desc_mn(smem_u32(smem + OFF_Q), 8192), dDOmn = desc_mn(smem_u32(smem + OFF_DO), 8192),
-                           dPTd = desc_k(smem_u32(smem + OFF_PT)), dDSTd = desc_k(smem_u32(smem + OFF_DST));
+                           dQmn = desc_mn(smem_u32(smem + OFF_Q), 8192), dDOmn = desc_mn(smem_u32(smem + OFF_DO), 8192);
             ATT_WAIT(kv_full, 0, DS_TIMEOUT_MMA);
-            for (int it = -2; it < iters; it++) {   // S^T / dP^T run two sub-tiles ahead
-                if (it + 2 < iters) {
-                    const int in = it + 2, st = in & 1, qs_ = in % QST;
-                    ATT_WAIT(&qdo_full[qs_], (in / QST) & 1, DS_TIMEOUT_MMA);
-                    ATT_WAIT(&s_empty[st], ((in >> 1) & 1) ^ 1u, DS_TIMEOUT_MMA);
-                    tcgen05_fence_after_sync();
-                    mma_kk<HD, 64>(TM_ST + st * 64, dKd, 16384, dQk + ((qs_ * TB64) >> 4), 8192, false);     // S^T  = K . Q^T
-                    mma_kk<HD, 64>(TM_DPT + st * 64, dVd, 16384, dDOk + ((qs_ * TB64) >> 4), 8192, false);   // dP^T = V . dO^T
-                    umma_commit(&s_full[st]);
-                }
-                if (it >= 0) {
-                    const int qs_ = it % QST;
-                    ATT_WAIT(p_full, it & 1, DS_TIMEOUT_MMA);
-                    tcgen05_fence_after_sync();
-                    mma_kmn<HD, 64>(TM_DV, dPTd, dDOmn + ((qs_ * TB64) >> 4), it > 0);    // dV += P^T . dO
-                    mma_kmn<HD, 64>(TM_DK, dDSTd, dQmn + ((qs_ * TB64) >> 4), it > 0);    // dK += dS^T . Q
-                    umma_commit(&qdo_empty[qs_]);
-                    umma_commit(p_empty);
-                }
+            auto scores = [&](int in) -> bool {      // S^T = K . Q^T and dP^T = V . dO^T of sub-tile `in`
+                const int st = in & 1, qs_ = in % QST;
+                if (!mbar_wait(&qdo_full[qs_], (in / QST) & 1, abort_flag, p.status, DS_TIMEOUT_MMA)) return false;
+                tcgen05_fence_after_sync();
+                mma_kk<HD, 64>(TM_ST + st * 64, dKd, 16384, dQk + ((qs_ * TB64) >> 4), 8192, false);
+                mma_kk<HD, 64>(TM_DPT + st * 64, dVd, 16384, dDOk + ((qs_ * TB64) >> 4), 8192, false);
+                umma_commit(&s_full[st]);
+                return true;
+            };
+            for (int in = 0; in < 2 && in < iters; in++)
+                if (!scores(in)) goto done;
+            for (int it = 0; it < iters; it++) {
+                const int qs_ = it % QST, st = it & 1;
+                ATT_WAIT(&p_full[st], (it >> 1) & 1, DS_TIMEOUT_MMA);   // P^T, dS^T of sub-tile it are in TMEM
+                tcgen05_fence_after_sync();
+                mma_tmn<HD, 64>(TM_DV, TM_ST + st * 64, dDOmn + ((qs_ * TB64) >> 4), it > 0);     // dV += P^T . dO
+                mma_tmn<HD, 64>(TM_DK, TM_DPT + st * 64, dQmn + ((qs_ * TB64) >> 4), it > 0);     // dK += dS^T . Q
+                umma_commit(&qdo_empty[qs_]);
+                if (it + 2 < iters && !scores(it + 2)) goto done;      // reuses the S^T / dP^T buffers just read
             }
             umma_commit(acc_full);
         }
@@ -683,9 +697,6 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
                 tmem_ld_x32(TM_DPT + st * 64 + lane_addr + c * 32, rp[c]);
             }
             tmem_ld_wait();
-            tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[st]);
             const bool diag = (qs * 64 < kv0 + 127);
 #pragma unroll
             for (int c = 0; c < 2; c++)
@@ -711,19 +722,13 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
                     dk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * (__uint_as_float(rp[c][i]) - dlt[col]) * p.scale,
                                                         p1 * (__uint_as_float(rp[c][i + 1]) - dlt[col + 1]) * p.scale);
                 }
-            ATT_WAIT(p_empty, (it & 1) ^ 1u, DS_TIMEOUT_SOFTMAX);   // dV/dK of the previous sub-tile have read P^T, dS^T
-            uint8_t* sPT = smem + OFF_PT;
-            uint8_t* sDST = smem + OFF_DST;
-#pragma unroll
-            for (int g = 0; g < 8; g++) {
-                const uint32_t off = kmajor_off(row, g * 8);
-                *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-                *reinterpret_cast<uint4*>(sDST + off) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
-            }
-            fence_proxy_async_smem();
+            // P^T and dS^T go back into this thread's own rows of the S^T / dP^T buffers (first 32 columns)
+            tmem_st_x32(TM_ST + st * 64 + lane_addr, pk);
+            tmem_st_x32(TM_DPT + st * 64 + lane_addr, dk);
+            tmem_st_wait();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(&p_full[st]);
         }
         ATT_WAIT(acc_full, 0, DS_TIMEOUT_SOFTMAX);
         tcgen05_fence_after_sync();
@@ -761,7 +766,7 @@ done:
 
 template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 2 * 32768 + 256 + 1024; }
 template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 2 * kDqStages * Tile<HD>::BYTES64 + 32768 + 256 + 1024; }
-template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 32768 + 1024 + 256 + 1024; }
+template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 1024 + 256 + 1024; }
 
 int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const void* V, const void* dO, int B, int T,
               int Hq, int Hkv, int hd) {
