@@ -399,6 +399,9 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __
 // ─────────────────────────────── backward: dQ ───────────────────────────────
 // CTA = 128 query rows of one head; keys are walked in sub-tiles of 64 so that S and dP can be double
 // buffered in TMEM: S[2] at columns [0,128), dP[2] at [128,256), dQ accumulator at [256, 256+HD).
+// dS never touches shared memory: each element-wise thread overwrites the first 32 columns of its dP row
+// with the BF16 pairs and dQ += dS.K reads that A operand from TMEM (the tensor pipe executes in issue
+// order, so the scores of sub-tile j+2, issued after dQ of sub-tile j, cannot overwrite a dS still in use).
 
 template <int HD>
 __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
@@ -406,13 +409,13 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
     constexpr int KVST = kDqStages;   // K/V ring depth: a stage is only released after dQ += dS.K, so the
                                       // prefetch distance must cover the TMA latency
     constexpr uint32_t OFF_Q = 0, OFF_DO = TB, OFF_K = 2 * TB, OFF_V = 2 * TB + KVST * TB64,
-                       OFF_DS = 2 * TB + 2 * KVST * TB64, OFF_BAR = OFF_DS + 32768;
+                       OFF_BAR = 2 * TB + 2 * KVST * TB64;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t *qdo_full = bars, *kv_full = bars + 1, *kv_empty = bars + 1 + KVST, *s_full = bars + 1 + 2 * KVST,
-             *s_empty = s_full + 2, *ds_full = s_full + 4, *ds_empty = s_full + 6, *dq_full = s_full + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 9);
+             *ds_full = s_full + 2, *dq_full = s_full + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -427,8 +430,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
         mbar_init(qdo_full, 1);
         for (int i = 0; i < KVST; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
-            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
-            mbar_init(&ds_full[i], 4); mbar_init(&ds_empty[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&ds_full[i], 4);
         }
         mbar_init(dq_full, 1);
         *abort_flag = 0;
@@ -458,26 +460,26 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
         if (lane == 0) {
             const uint64_t dQd = desc_k(smem_u32(smem + OFF_Q)), dDOd = desc_k(smem_u32(smem + OFF_DO)),
                            dKk = desc_k(smem_u32(smem + OFF_K)), dVk = desc_k(smem_u32(smem + OFF_V)),
-                           dKmn = desc_mn(smem_u32(smem + OFF_K), 8192), dDSd = desc_k(smem_u32(smem + OFF_DS));
+                           dKmn = desc_mn(smem_u32(smem + OFF_K), 8192);
             ATT_WAIT(qdo_full, 0, DS_TIMEOUT_MMA);
-            for (int j = -2; j < n; j++) {   // S / dP run two sub-tiles ahead of the element-wise warps
-                if (j + 2 < n) {
-                    const int jn = j + 2, st = jn & 1, ks = jn % KVST;
-                    ATT_WAIT(&kv_full[ks], (jn / KVST) & 1, DS_TIMEOUT_MMA);
-                    ATT_WAIT(&s_empty[st], ((jn >> 1) & 1) ^ 1u, DS_TIMEOUT_MMA);
-                    tcgen05_fence_after_sync();
-                    mma_kk<HD, 64>(TM_S + st * 64, dQd, 16384, dKk + ((ks * TB64) >> 4), 8192, false);
-                    mma_kk<HD, 64>(TM_DP + st * 64, dDOd, 16384, dVk + ((ks * TB64) >> 4), 8192, false);
-                    umma_commit(&s_full[st]);
-                }
-                if (j >= 0) {
-                    const int st = j & 1, ks = j % KVST;
-                    ATT_WAIT(&ds_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
-                    tcgen05_fence_after_sync();
-                    mma_kmn<HD, 64>(TM_DQ, dDSd + ((st * 16384) >> 4), dKmn + ((ks * TB64) >> 4), j > 0);
-                    umma_commit(&kv_empty[ks]);
-                    umma_commit(&ds_empty[st]);
-                }
+            auto scores = [&](int jn) -> bool {      // S = Q . K^T and dP = dO . V^T of key sub-tile jn
+                const int st = jn & 1, ks = jn % KVST;
+                if (!mbar_wait(&kv_full[ks], (jn / KVST) & 1, abort_flag, p.status, DS_TIMEOUT_MMA)) return false;
+                tcgen05_fence_after_sync();
+                mma_kk<HD, 64>(TM_S + st * 64, dQd, 16384, dKk + ((ks * TB64) >> 4), 8192, false);
+                mma_kk<HD, 64>(TM_DP + st * 64, dDOd, 16384, dVk + ((ks * TB64) >> 4), 8192, false);
+                umma_commit(&s_full[st]);
+                return true;
+            };
+            for (int jn = 0; jn < 2 && jn < n; jn++)
+                if (!scores(jn)) goto done;
+            for (int j = 0; j < n; j++) {
+                const int st = j & 1, ks = j % KVST;
+                ATT_WAIT(&ds_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);   // dS of sub-tile j is in TMEM
+                tcgen05_fence_after_sync();
+                mma_tmn<HD, 64>(TM_DQ, TM_DP + st * 64, dKmn + ((ks * TB64) >> 4), j > 0);   // dQ += dS . K
+                umma_commit(&kv_empty[ks]);
+                if (j + 2 < n && !scores(j + 2)) goto done;            // reuses the S / dP buffers just read
             }
             umma_commit(dq_full);
         }
@@ -502,9 +504,6 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
                 tmem_ld_x32(TM_DP + st * 64 + lane_addr + c * 32, rp[c]);
             }
             tmem_ld_wait();
-            tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[st]);
             const bool diag = (j * 64 + 63 > q0);
             // staged so that the 64 special-function ops issue back to back (see the forward kernel)
 #pragma unroll
@@ -527,13 +526,8 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
                     pk[c * 16 + (i >> 1)] =
                         pack_bf16x2(__uint_as_float(rs[c][i]) * (__uint_as_float(rp[c][i]) - dlt) * p.scale,
                                     __uint_as_float(rs[c][i + 1]) * (__uint_as_float(rp[c][i + 1]) - dlt) * p.scale);
-            ATT_WAIT(&ds_empty[st], ph ^ 1u, DS_TIMEOUT_SOFTMAX);
-            uint8_t* sDS = smem + OFF_DS + st * 16384;
-#pragma unroll
-            for (int g = 0; g < 8; g++)
-                *reinterpret_cast<uint4*>(sDS + kmajor_off(row, g * 8)) =
-                    make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-            fence_proxy_async_smem();
+            tmem_st_x32(TM_DP + st * 64 + lane_addr, pk);   // dS back into this thread's dP row (first 32 columns)
+            tmem_st_wait();
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ds_full[st]);
@@ -765,7 +759,7 @@ done:
 }
 
 template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 2 * 32768 + 256 + 1024; }
-template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 2 * kDqStages * Tile<HD>::BYTES64 + 32768 + 256 + 1024; }
+template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 2 * kDqStages * Tile<HD>::BYTES64 + 256 + 1024; }
 template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 1024 + 256 + 1024; }
 
 int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const void* V, const void* dO, int B, int T,
