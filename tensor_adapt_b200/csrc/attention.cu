@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __
 // order, so the scores of sub-tile j+2, issued after dQ of sub-tile j, cannot overwrite a dS still in use).
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
     constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
     constexpr int KVST = kDqStages;   // K/V ring depth: a stage is only released after dQ += dS.K, so the
                                       // prefetch distance must cover the TMA latency
@@ -418,6 +418,10 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+    if (blockDim.x != 320) {   // the warp roles below assume ten warps: refuse any other launch shape
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, int(DS_BAD_LAUNCH));
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nt = (p.T + 127) / 128, hb = p.Hq * p.B;
     const int qt = nt - 1 - int(blockIdx.x) / hb;   // heavy-first over the whole launch
@@ -484,7 +488,9 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
             umma_commit(dq_full);
         }
     } else {
-        const int lg = warp & 3;
+        // Two groups of four element-wise warps: group g owns the key sub-tiles of parity g with the S / dP
+        // buffers of that parity; dQ is a plain sum, so both groups feed the same accumulator.
+        const int lg = warp & 3, grp = (warp - 2) >> 2;
         const int row = lg * 32 + lane;
         const int q_idx = q0 + row;
         const bool ok = q_idx < p.T;
@@ -492,8 +498,8 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
         const size_t stat = (size_t(b) * p.Hq + h) * p.T + q_idx;
         const float lse2 = ok ? p.lse[stat] * kLog2e : INFINITY;
         const float dlt = ok ? p.delta[stat] : 0.f;
-        for (int j = 0; j < n; j++) {
-            const int st = j & 1;
+        for (int j = grp; j < n; j += 2) {
+            const int st = grp;
             const uint32_t ph = (j >> 1) & 1;
             ATT_WAIT(&s_full[st], ph, DS_TIMEOUT_SOFTMAX);
             tcgen05_fence_after_sync();
@@ -536,7 +542,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
         tcgen05_fence_after_sync();
         __nv_bfloat16* orow = p.out + (size_t(b) * p.T + q_idx) * (size_t(p.Hq) * HD) + h * HD;
 #pragma unroll
-        for (int c = 0; c < HD / 32; c++) {
+        for (int c = grp * (HD / 64); c < (grp + 1) * (HD / 64); c++) {   // each group stores half of the head dimension
             uint32_t r[32];
             tmem_ld_x32(TM_DQ + lane_addr + c * 32, r);
             tmem_ld_wait();
@@ -569,20 +575,22 @@ done:
 // overwrite a P^T that is still being read.
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(320, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
     constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
     constexpr int QST = kDkvStages;   // Q/dO ring depth (a stage is released only after dV, dK consumed it)
-    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + QST * TB64, OFF_STAT = 2 * TB + 2 * QST * TB64,
-                       OFF_BAR = OFF_STAT + 1024;
+    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + QST * TB64, OFF_BAR = 2 * TB + 2 * QST * TB64;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 1 + QST, *s_full = bars + 1 + 2 * QST,
-             *p_full = s_full + 2, *acc_full = s_full + 4, *stat_full = s_full + 5;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 6);
+             *p_full = s_full + 2, *acc_full = s_full + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* stat = reinterpret_cast<float*>(smem + OFF_STAT);   // [2 buffers][lse2 64 | delta 64]
 
+    if (blockDim.x != 320) {   // the warp roles below assume ten warps: refuse any other launch shape
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, int(DS_BAD_LAUNCH));
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hbk = p.Hkv * p.B;
     const int kt = int(blockIdx.x) / hbk;   // key tile 0 has the most work: all its CTAs start first
@@ -594,7 +602,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
     const int kv0 = kt * 128;
 
     if (threadIdx.x == 0) {
-        mbar_init(kv_full, 1); mbar_init(acc_full, 1); mbar_init(stat_full, 2);
+        mbar_init(kv_full, 1); mbar_init(acc_full, 1);
         for (int i = 0; i < QST; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
             mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4);
@@ -651,37 +659,36 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
             umma_commit(acc_full);
         }
     } else {
-        const int lg = warp & 3;
+        // Two groups of four element-wise warps: group g owns the query sub-tiles of parity g with the
+        // S^T / dP^T buffers of that parity; dK and dV are plain sums, so both groups feed the same
+        // accumulators.  The per-query statistics (lse, delta) of a sub-tile are 64 values shared by every key
+        // row: each warp keeps them two per lane and broadcasts them with shuffles.
+        const int lg = warp & 3, grp = (warp - 2) >> 2;
         const int row = lg * 32 + lane;     // key row of this thread
-        const int tid = threadIdx.x - 64;   // 0..127 among the compute threads
         const int kv_idx = kv0 + row;
         const uint32_t lane_addr = uint32_t(lg * 32) << 16;
-        // per-query statistics are fetched one iteration ahead so their global-memory latency hides
-        // behind the element-wise work of the current iteration
-        auto fetch = [&](int it, float& fl, float& fd) {
-            fl = INFINITY; fd = 0.f;   // +inf -> probability 0 for padded queries
-            if (tid < 64 && it < iters) {
-                const int h = hk * G + it / per_head, q = (2 * kt + it % per_head) * 64 + tid;
-                if (q < p.T) {
-                    const size_t si = (size_t(b) * p.Hq + h) * p.T + q;
-                    fl = p.lse[si] * kLog2e; fd = p.delta[si];
+        // fetched one of the group's iterations ahead so the global-memory latency hides behind the
+        // element-wise work of the current one; +inf -> probability 0 for padded queries
+        auto fetch = [&](int it, float (&fl)[2], float (&fd)[2]) {
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                fl[k] = INFINITY; fd[k] = 0.f;
+                if (it < iters) {
+                    const int h = hk * G + it / per_head, q = (2 * kt + it % per_head) * 64 + k * 32 + lane;
+                    if (q < p.T) {
+                        const size_t si = (size_t(b) * p.Hq + h) * p.T + q;
+                        fl[k] = p.lse[si] * kLog2e; fd[k] = p.delta[si];
+                    }
                 }
             }
         };
-        float next_l, next_d;
-        fetch(0, next_l, next_d);
-        for (int it = 0; it < iters; it++) {
-            const int qs = 2 * kt + it % per_head, st = it & 1;
+        float next_l[2], next_d[2];
+        fetch(grp, next_l, next_d);
+        for (int it = grp; it < iters; it += 2) {
+            const int qs = 2 * kt + it % per_head, st = grp;
             const uint32_t ph = (it >> 1) & 1;
-            float* lse2 = stat + st * 128;
-            float* dlt = lse2 + 64;
-            if (tid < 64) { lse2[tid] = next_l; dlt[tid] = next_d; }
-            fetch(it + 1, next_l, next_d);
-            // the two warps that wrote the 64 entries of lse / delta publish them: one elected arrival each
-            // (an arrival per thread would be 128 serialised shared-memory atomics per sub-tile)
-            __syncwarp();
-            if (tid < 64 && lane == 0) mbar_arrive(stat_full);
-            ATT_WAIT(stat_full, it & 1, DS_TIMEOUT_SOFTMAX);
+            const float cl[2] = {next_l[0], next_l[1]}, cd[2] = {next_d[0], next_d[1]};
+            fetch(it + 2, next_l, next_d);
             ATT_WAIT(&s_full[st], ph, DS_TIMEOUT_SOFTMAX);
             tcgen05_fence_after_sync();
             uint32_t rs[2][32], rp[2][32];
@@ -692,29 +699,21 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
             }
             tmem_ld_wait();
             const bool diag = (qs * 64 < kv0 + 127);
-#pragma unroll
-            for (int c = 0; c < 2; c++)
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const int col = c * 32 + i;
-                    float a = __uint_as_float(rs[c][i]) * p.scale_log2 - lse2[col];
-                    if (diag && (kv_idx > qs * 64 + col)) a = -INFINITY;
-                    rs[c][i] = __float_as_uint(a);
-                }
-#pragma unroll
-            for (int c = 0; c < 2; c++)
-#pragma unroll
-                for (int i = 0; i < 32; i++) rs[c][i] = __float_as_uint(ex2_approx(__uint_as_float(rs[c][i])));
             uint32_t pk[32], dk[32];
 #pragma unroll
             for (int c = 0; c < 2; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const int col = c * 32 + i;
-                    const float p0 = __uint_as_float(rs[c][i]), p1 = __uint_as_float(rs[c][i + 1]);
+                    float a0 = __uint_as_float(rs[c][i]) * p.scale_log2 - __shfl_sync(0xffffffffu, cl[c], i);
+                    float a1 = __uint_as_float(rs[c][i + 1]) * p.scale_log2 - __shfl_sync(0xffffffffu, cl[c], i + 1);
+                    if (diag && (kv_idx > qs * 64 + col)) a0 = -INFINITY;
+                    if (diag && (kv_idx > qs * 64 + col + 1)) a1 = -INFINITY;
+                    const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
                     pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
-                    dk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * (__uint_as_float(rp[c][i]) - dlt[col]) * p.scale,
-                                                        p1 * (__uint_as_float(rp[c][i + 1]) - dlt[col + 1]) * p.scale);
+                    dk[c * 16 + (i >> 1)] =
+                        pack_bf16x2(p0 * (__uint_as_float(rp[c][i]) - __shfl_sync(0xffffffffu, cd[c], i)) * p.scale,
+                                    p1 * (__uint_as_float(rp[c][i + 1]) - __shfl_sync(0xffffffffu, cd[c], i + 1)) * p.scale);
                 }
             // P^T and dS^T go back into this thread's own rows of the S^T / dP^T buffers (first 32 columns)
             tmem_st_x32(TM_ST + st * 64 + lane_addr, pk);
@@ -728,8 +727,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
         tcgen05_fence_after_sync();
         const bool ok = kv_idx < p.T;
         const size_t ro = (size_t(b) * p.T + kv_idx) * (size_t(p.Hkv) * HD) + hk * HD;
-#pragma unroll
-        for (int which = 0; which < 2; which++) {
+        for (int which = grp; which <= grp; which++) {   // group 0 stores dV, group 1 stores dK
             __nv_bfloat16* orow = (which == 0 ? p.out3 : p.out2) + ro;
             const uint32_t ta = (which == 0 ? TM_DV : TM_DK) + lane_addr;
 #pragma unroll
@@ -760,7 +758,7 @@ done:
 
 template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 2 * 32768 + 256 + 1024; }
 template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 2 * kDqStages * Tile<HD>::BYTES64 + 256 + 1024; }
-template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 1024 + 256 + 1024; }
+template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 256 + 1024; }
 
 int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const void* V, const void* dO, int B, int T,
               int Hq, int Hkv, int hd) {
@@ -853,16 +851,16 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
     ProfScope prof(ctx, s, PROF_ATTN_BWD, 5.0 * 2.0 * B * Hq * double(T) * T * head_dim * 0.5);
     if (head_dim == 128) {
         if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<128>, dkv_smem<128>())) return rc;
-        attn_bwd_dkv_kernel<128><<<dim3(nt * Hkv * B), 192, dkv_smem<128>(), s>>>(p);
+        attn_bwd_dkv_kernel<128><<<dim3(nt * Hkv * B), 320, dkv_smem<128>(), s>>>(p);
         TA_LAUNCH_CHECK(ctx, "attn_bwd_dkv_kernel");
         if (int rc = set_smem(ctx, attn_bwd_dq_kernel<128>, dq_smem<128>())) return rc;
-        attn_bwd_dq_kernel<128><<<dim3(nt * Hq * B), 192, dq_smem<128>(), s>>>(p);
+        attn_bwd_dq_kernel<128><<<dim3(nt * Hq * B), 320, dq_smem<128>(), s>>>(p);
     } else {
         if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<64>, dkv_smem<64>())) return rc;
-        attn_bwd_dkv_kernel<64><<<dim3(nt * Hkv * B), 192, dkv_smem<64>(), s>>>(p);
+        attn_bwd_dkv_kernel<64><<<dim3(nt * Hkv * B), 320, dkv_smem<64>(), s>>>(p);
         TA_LAUNCH_CHECK(ctx, "attn_bwd_dkv_kernel");
         if (int rc = set_smem(ctx, attn_bwd_dq_kernel<64>, dq_smem<64>())) return rc;
-        attn_bwd_dq_kernel<64><<<dim3(nt * Hq * B), 192, dq_smem<64>(), s>>>(p);
+        attn_bwd_dq_kernel<64><<<dim3(nt * Hq * B), 320, dq_smem<64>(), s>>>(p);
     }
     TA_LAUNCH_CHECK(ctx, "attn_bwd_dq_kernel");
     return TA_OK;
