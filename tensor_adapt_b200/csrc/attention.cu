@@ -11,8 +11,10 @@
 //   attn_bwd_dkv_kernel CTA = (128 key rows, KV head, batch); dK, dV accumulate in TMEM over all query
 //                       tiles AND all query heads of the GQA group, so no atomics are needed
 //
-// 192 threads per CTA: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = softmax / element-wise
-// work with one thread per tile row (TMEM lane).  Every wait is bounded.
+// 320 threads per CTA: warp 0 = TMA producer, warp 1 = MMA issuer (one elected thread), warps 2-9 = two
+// groups of four softmax / element-wise warps (one thread per tile row = TMEM lane) that work on
+// alternating key tiles / sub-tiles.  In the backward kernels the second contractions read their A operand
+// (dS, P^T, dS^T) straight from tensor memory.  Every wait is bounded.
 #include <algorithm>
 #include <cmath>
 
