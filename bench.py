@@ -219,9 +219,19 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
-        # NCCL writes its version / debug lines to stdout by default; stdout carries the one JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # NCCL prints its version line on stdout when the communicator is created; stdout carries the one JSON
+        # line only, so file descriptor 1 points at stderr while the process group comes up
+        sys.stdout.flush()
+        saved_fd = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_fd, 1)
+            os.close(saved_fd)
     model, lrank, alpha, targets, T, gbatch, micro = CONFIGS[args.config]
     if args.micro_batch:
         micro = args.micro_batch
