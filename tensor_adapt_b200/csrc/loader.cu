@@ -177,10 +177,9 @@ bool parse_json(const char* text, size_t n, Json* out, std::string* err) {
 struct Sha256 {
     uint32_t h[8] = {0x6a09e667u, 0xbb67ae85u, 0x3c6ef372u, 0xa54ff53au, 0x510e527fu, 0x9b05688cu, 0x1f83d9abu, 0x5be0cd19u};
     static uint32_t rotr(uint32_t x, int n) { return (x >> n) | (x << (32 - n)); }
-    static const uint32_t* K() {
-        static uint32_t k[64];
-        static bool init = false;
-        if (!init) {   // fractional parts of the cube roots of the first 64 primes
+    struct RoundConstants {
+        uint32_t k[64];
+        RoundConstants() {   // fractional parts of the cube roots of the first 64 primes
             int n = 0;
             for (int c = 2; n < 64; c++) {
                 bool prime = true;
@@ -189,9 +188,11 @@ struct Sha256 {
                 const long double r = cbrtl((long double)c);
                 k[n++] = uint32_t((r - floorl(r)) * 4294967296.0L);
             }
-            init = true;
         }
-        return k;
+    };
+    static const uint32_t* K() {
+        static const RoundConstants rc;   // initialised once, thread-safe
+        return rc.k;
     }
     void block(const unsigned char* b) {
         const uint32_t* k = K();
