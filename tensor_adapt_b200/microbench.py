@@ -6,6 +6,7 @@ with ncu; the summaries under profiles/ name the exact command lines).
     python -m tensor_adapt_b200.microbench rowops --rows 16384 --D 3584 --I 18944
     python -m tensor_adapt_b200.microbench lora --BT 4096 --in 896 --out 896 --rank 16
     python -m tensor_adapt_b200.microbench skinny --BT 16384 --in 3584 --out 18944 --rank 16
+    python -m tensor_adapt_b200.microbench kmeans --N 2048 --D 512 --k 8
 
 Each line reports the median of `--iters` launches after `--warmup`; inputs are larger than L2 or the
 L2 is flushed between launches (a 256 MB buffer is rewritten) when `--flush` is given.
@@ -111,6 +112,27 @@ def skinny(ctx, a):
     report("gA += dh^T.x", t, bytes_=2.0 * BT * (ind + r), shape=[ind, r, BT])
 
 
+def kmeans(ctx, a):
+    """Centroid merge (BASELINE config 1 shape by default): reference-mode k-means and the seeded
+    k-means++ / mass-ranked extension, whole call including its per-pass host synchronisation."""
+    import ctypes
+    N, D, k = a.N, a.D, a.k
+    g = torch.Generator(device="cuda").manual_seed(0)
+    centres = torch.randn(12, D, device="cuda", generator=g)
+    vec = (centres[torch.randint(0, 12, (N,), device="cuda", generator=g)] + 0.1 * torch.randn(N, D, device="cuda", generator=g)).contiguous()
+    mass = torch.rand(N, device="cuda", generator=g) + 0.1
+    kk = min(k, N)
+    cen, asg = torch.zeros(kk, D, device="cuda"), torch.zeros(N, dtype=torch.int32, device="cuda")
+    kout, passes = ctypes.c_int(0), ctypes.c_int(0)
+    f = lambda: ctx.call("ta_kmeans_merge", ptr(vec), N, D, k, 50, ptr(cen), ptr(asg), ctypes.byref(kout), ctypes.byref(passes), stream_ptr())
+    t = timeit(f, a.iters, a.warmup, False)
+    report("kmeans_merge (reference mode)", t, shape=[N, D, k], passes=passes.value)
+    f2 = lambda: ctx.call("ta_kmeans_merge_ex", ptr(vec), ptr(mass), N, D, k, 50, 1, 7, 1, ptr(cen), ptr(asg), None, None,
+                          ctypes.byref(kout), ctypes.byref(passes), stream_ptr())
+    t = timeit(f2, a.iters, a.warmup, False)
+    report("kmeans_merge_ex (k-means++ start, mass ranking)", t, shape=[N, D, k], passes=passes.value)
+
+
 def rowops(ctx, a):
     rows, D, I = a.rows, a.D, a.I
     x, w, dy = rnd(rows, D), rnd(D), rnd(rows, D)
@@ -138,7 +160,7 @@ def rowops(ctx, a):
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention", "gemm", "lora", "rowops", "skinny"):
+    for name in ("attention", "gemm", "lora", "rowops", "skinny", "kmeans"):
         s = sub.add_parser(name)
         s.add_argument("--iters", type=int, default=10); s.add_argument("--warmup", type=int, default=3)
         s.add_argument("--flush", action="store_true")
@@ -149,6 +171,9 @@ def main():
             for k, v in (("M", 16384), ("N", 3584), ("K", 3584)):
                 s.add_argument("--" + k, type=int, default=v)
             s.add_argument("--b-layout", type=int, default=0)
+        elif name == "kmeans":
+            for k, v in (("N", 2048), ("D", 512), ("k", 8)):
+                s.add_argument("--" + k, type=int, default=v)
         elif name in ("lora", "skinny"):
             for k, v in (("BT", 4096), ("in", 896), ("out", 896), ("rank", 16)):
                 s.add_argument("--" + k, type=int, default=v)
@@ -157,7 +182,7 @@ def main():
                 s.add_argument("--" + k, type=int, default=v)
     a = ap.parse_args()
     ctx = ta.Context(0)
-    {"attention": attention, "gemm": gemm, "lora": lora, "rowops": rowops, "skinny": skinny}[a.what](ctx, a)
+    {"attention": attention, "gemm": gemm, "lora": lora, "rowops": rowops, "skinny": skinny, "kmeans": kmeans}[a.what](ctx, a)
     torch.cuda.synchronize()
     ctx.check_device()
 
