@@ -62,7 +62,10 @@ def check_grads(got, ref, label):
 
 
 @pytest.mark.parametrize("targets,rank,hd", [(("q", "k", "v", "o"), 16, 64), (o.ALL_TARGETS, 16, 128),
-                                              (("q", "k", "v", "o"), 4, 64), (o.ALL_TARGETS, 64, 64)])
+                                              (("q", "k", "v", "o"), 4, 64), (o.ALL_TARGETS, 64, 64),
+                                              # partial groups: q/k/v and gate/up only share one h / dh / gA pass when all
+                                              # members are adapted, otherwise every projection goes alone
+                                              (("q", "v", "up", "down"), 16, 64), (("k", "gate"), 16, 128)])
 def test_step_vs_oracle(ctx, targets, rank, hd):
     cfg = rc.tiny_cfg(hd=hd, hq=4, hkv=2, hidden=4 * hd)
     B, T, alpha, lr = 2, 128, 2.0 * rank, 2e-4
