@@ -88,3 +88,38 @@ def test_probe_errors(tmp_path):
         open(p, "wb").write(mutate(raw))
         with pytest.raises(TAError, match=msg):
             probe_base(d)
+
+
+def test_probe_survives_corrupted_headers(tmp_path):
+    """Byte-level corruption of a valid safetensors header (flipped bytes, truncations, random lengths) must
+    end in a clean success or a TAError - never a crash or a hang: the header is untrusted input."""
+    from tensor_adapt_b200 import TAError
+    from tensor_adapt_b200.trainer import probe_base
+    cfg, base = _tiny()
+    d = str(tmp_path / "m")
+    o.write_hf_dir(d, cfg, base)
+    p = os.path.join(d, "model.safetensors")
+    raw = open(p, "rb").read()
+    hlen = struct.unpack("<Q", raw[:8])[0]
+    rng = np.random.default_rng(0)
+    outcomes = {"ok": 0, "err": 0}
+    for trial in range(300):
+        b = bytearray(raw[:8 + hlen + 4096])           # header + a little data is enough for the parser
+        kind = trial % 4
+        if kind == 0:                                   # flip a few header bytes
+            for _ in range(int(rng.integers(1, 6))):
+                b[8 + int(rng.integers(0, hlen))] = int(rng.integers(0, 256))
+        elif kind == 1:                                 # truncate inside the header
+            b = b[:8 + int(rng.integers(0, hlen))]
+        elif kind == 2:                                 # lie about the header length
+            b[:8] = struct.pack("<Q", int(rng.integers(0, 2 * len(b))))
+        else:                                           # splice structural characters in
+            pos = 8 + int(rng.integers(0, hlen))
+            b[pos:pos] = bytes(rng.choice(list(b'{}[]",:\\'), size=int(rng.integers(1, 8))).tolist())
+        open(p, "wb").write(bytes(b))
+        try:
+            probe_base(d)
+            outcomes["ok"] += 1
+        except TAError:
+            outcomes["err"] += 1
+    assert outcomes["err"] > 100 and outcomes["ok"] + outcomes["err"] == 300
