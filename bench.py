@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config qwen2-7b]
 
-One "step" is one optimiser step over the GLOBAL batch of BASELINE config 5 (Qwen2-7B shapes, random
+One "step" is one optimiser step over the GLOBAL batch of the headline configuration (Qwen2-7B shapes, random
 BF16 weights, LoRA r=16 alpha=32 on all seven projections, 32 sequences x 4096 uniform-random ids,
 centroid accumulator on): zero_grad, forward, cross-entropy, backward, centroid accumulation,
 grad-norm / clip / AdamW.  The global batch is fixed as N grows (strong scaling): each rank takes
@@ -42,6 +42,15 @@ CONFIGS = {
     "qwen2-7b": ("qwen2-7b", 16, 32.0, 127, 4096, 32, 4),
     "qwen2-1.5b": ("qwen2-1.5b", 64, 128.0, 127, 2048, 16, 8),
     "qwen2-0.5b": ("qwen2-0.5b", 16, 32.0, 15, 1024, 8, 8),
+}
+
+
+# Model shapes as plain tuples (vocab, hidden, layers, q_heads, kv_heads, head_dim, intermediate, tied head):
+# the reference arm and the CPU baseline read these, so neither has to load the CUDA library.
+SHAPES = {
+    "qwen2-0.5b": (151936, 896, 24, 14, 2, 64, 4864, 1),
+    "qwen2-1.5b": (151936, 1536, 28, 12, 2, 128, 8960, 1),
+    "qwen2-7b": (152064, 3584, 28, 28, 4, 128, 18944, 0),
 }
 
 
@@ -118,12 +127,10 @@ def cpu_baseline(cfg_name):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import numpy as np
     import ta_oracle as o
-    from tensor_adapt_b200.trainer import QWEN2
     model, rank, alpha, targets, T, _, _ = CONFIGS[cfg_name]
-    mc = QWEN2[model]
+    vocab, hidden, layers, hq, hkv, hd, inter, tie = SHAPES[model]
     T = 256
-    cfg = o.BaseConfig(vocab=mc.vocab, hidden=mc.hidden, layers=1, hq=mc.q_heads, hkv=mc.kv_heads, hd=mc.head_dim,
-                       inter=mc.intermediate, tie=bool(mc.tie_embeddings))
+    cfg = o.BaseConfig(vocab=vocab, hidden=hidden, layers=1, hq=hq, hkv=hkv, hd=hd, inter=inter, tie=bool(tie))
     rng = np.random.default_rng(0)
     base = o.make_base(cfg, rng)
     tnames = [t for b, t in enumerate(o.ALL_TARGETS) if targets & (1 << b)]
@@ -143,14 +150,14 @@ def cpu_baseline(cfg_name):
     o.proj_fwd(lm, fwd["x_final"]); o.proj_bwd_x(lm, dlogits)
     t_head = (time.perf_counter() - th) + (t1 - t_head0)
     t_layer = max((t2 - t0) - t_head, 1e-6)
-    total = mc.layers * t_layer + t_head
+    total = layers * t_layer + t_head
     try:
         import threadpoolctl
         cores = max([p.get("num_threads", 1) for p in threadpoolctl.threadpool_info()] + [1])
     except Exception:
         cores = os.cpu_count() or 1
     return {"value": T / total, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": f"NumPy restatement, 1 of {mc.layers} layers + lm head of {model} shapes on {T} tokens "
+            "sample": f"NumPy restatement, 1 of {layers} layers + lm head of {model} shapes on {T} tokens "
                       f"(layer {t_layer:.2f}s, head {t_head:.2f}s), extrapolated to the full depth"}
 
 
@@ -159,8 +166,7 @@ def run_reference(args):
     if rank != 0:
         return
     model, lrank, alpha, _, T, _, _ = CONFIGS[args.config]
-    from tensor_adapt_b200.trainer import QWEN2
-    mc = QWEN2[model]
+    vocab, hidden, layers, hq, hkv, hd, inter, tie = SHAPES[model]
     harness = os.path.join(ROOT, "oracle", "_ref", "ref_harness")
     base = {"impl": "reference", "metric": "lora_train_tokens_per_s", "unit": "tokens/s", "higher_is_better": True}
     if not os.path.exists(harness):
@@ -170,8 +176,8 @@ def run_reference(args):
     B = {"qwen2-7b": 1, "qwen2-1.5b": 4, "qwen2-0.5b": 8}[args.config]
     d = tempfile.mkdtemp()
     with open(os.path.join(d, "cfg.txt"), "w") as f:
-        f.write(f"vocab {mc.vocab}\nhidden {mc.hidden}\nlayers {mc.layers}\nhq {mc.q_heads}\nhkv {mc.kv_heads}\n"
-                f"hd {mc.head_dim}\ninter {mc.intermediate}\neps 1e-6\ntheta 1e6\ntie {mc.tie_embeddings}\n"
+        f.write(f"vocab {vocab}\nhidden {hidden}\nlayers {layers}\nhq {hq}\nhkv {hkv}\n"
+                f"hd {hd}\ninter {inter}\neps 1e-6\ntheta 1e6\ntie {tie}\n"
                 f"rank {lrank}\nalpha {alpha}\nB {B}\nT {T}\nsteps {args.steps}\nwarmup_iters {args.warmup}\n"
                 f"centroid 1\nlr 2e-4\nwd 0.01\n")
     t0 = time.time()
@@ -186,6 +192,10 @@ def run_reference(args):
             "config": {"workload": f"{model} LoRA r{lrank} on q/k/v/o (the reference wires no other target), "
                                    f"{B} x {T} tokens per step, no gradient accumulation, centroid accumulator on; "
                                    "the reference's own CUDA build (it has no CPU implementation of this path)",
+                       "largest_feasible": True, "global_batch": B, "seq_len": T, "targets": "q,k,v,o",
+                       "why_not_the_headline_batch": "the reference materialises FP32 [B,Hq,T,T] per layer and indexes "
+                                                     "logits with 32-bit ints, so larger micro-batches do not run; it has "
+                                                     "no gradient accumulation, no gate/up/down adapters and no multi-GPU code",
                        "wall_s": round(time.time() - t0, 1)},
             "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": 1, "kind": "reference",
                              "sample": f"unmodified reference objects driven by oracle/ref_harness.cu, {B}x{T} tokens/step, "
@@ -248,6 +258,7 @@ def main():
     tr.torch_view("lora.master").add_(torch.randn(tr.tensor("lora.master")[2], device="cuda", generator=g) * 0.01)
     tr.sync_working()
     grad = tr.torch_view("lora.grad")
+    loss_stats = tr.torch_view("step.stats")[2:4]      # (sum of per-token losses, their count) of this rank's shard
 
     gen = np.random.default_rng(1234)
     host_batches, dev_batches = [], []
@@ -264,6 +275,7 @@ def main():
         tr.forward_backward(tok, tgt, b_local, global_tokens=global_tokens)
         if world > 1:
             dist.all_reduce(grad)
+            dist.all_reduce(loss_stats)                # so the reported loss is the global-batch mean on every rank
         return tr.optimizer_step(2e-4)
 
     def timed(n, host):

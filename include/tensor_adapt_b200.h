@@ -3,8 +3,8 @@
  * Drop-in boundary for carbon-os/tensor-adapt's CUDA backend and trainer: every entry point
  * below names the reference interface it replaces (file:line inside the reference tree).  The
  * reference has no FFI layer of its own; its boundary is the C++ API in include/tensor/, so each
- * function here is what a thin C++ shim with the reference's name and signature would call
- * (INTEGRATION.md shows those shims).
+ * function here is what a thin C++ shim with the reference's name and signature calls (the shim
+ * sources under shim/ implement the reference's own headers that way).
  *
  * Conventions
  *   - plain pointers and sizes only; `void*` data pointers are DEVICE pointers unless a parameter
@@ -50,6 +50,13 @@ const char* ta_last_error(const ta_ctx* ctx);
 int ta_device_status(ta_ctx* ctx, int* status);
 /* Kernels launched through this context so far. */
 long ta_launch_count(const ta_ctx* ctx);
+/* Experiment knob, no counterpart in the reference: force the GEMM tile (tile_n in {64,128,224,256},
+ * tile_m_halves 1 = 128-row or 2 = 256-row tiles; 0,0 = the built-in cost model) and / or select the
+ * CTA-pair kernel for 256-wide tiles.  Results are bit-identical for every choice.
+ * Threading: a context, and every object created from it, belongs to ONE host thread at a time (the
+ * reference's Device is single-threaded too); the library keeps per-device launch attributes and the
+ * static-scratch address in unsynchronised process-wide state that is written on first use. */
+int ta_ctx_set_gemm_tuning(ta_ctx* ctx, int tile_n, int tile_m_halves, int cta_pair);
 /* Optional CUDA-event timing of the tensor-core kernels, off by default (it adds two event records
  * per launch). Classes: 0 = segmented GEMM with tiles >= 128 wide, 1 = skinny GEMMs (rank-r and
  * split-K), 2 = attention forward, 3 = attention backward. ta_profile_read synchronises the device
@@ -357,9 +364,9 @@ int ta_dataset_seek(ta_dataset* ds, long position, long tokens_consumed);
  * into ids_dev / targets_dev [n_seq*T]. mask != 0 also applies the assistant-only target masking of
  * src/trainer/adapt_trainer.cu:145-182 in the same kernel. */
 int ta_dataset_next_batch(ta_dataset* ds, int B, int T, int first_seq, int n_seq, int* ids_dev, int* targets_dev, int mask,
-                          cudaStream_t stream);
+                          void* stream);
 /* The masking alone (src/trainer/adapt_trainer.cu:145-182) on device arrays; ta_mask_targets is the host form. */
-int ta_mask_targets_device(ta_ctx* ctx, const int* input_ids, int* target_ids, int B, int T, cudaStream_t stream);
+int ta_mask_targets_device(ta_ctx* ctx, const int* input_ids, int* target_ids, int B, int T, void* stream);
 /* AdaptTrainer::step as the reference runs it (do_step, src/trainer/adapt_trainer.cu:130-277: next_batch,
  * masking, zero_grad, forward, loss, backward, centroid, clip, AdamW) with the batch drawn on the device. */
 int ta_trainer_step_dataset(ta_trainer* tr, ta_dataset* ds, int B, int mask, float lr, long total_steps, ta_step_metrics* out);

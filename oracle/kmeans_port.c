@@ -4,7 +4,7 @@
  * host-side loops of the reference's Centroid Accumulator.  Only tests/, the smoke check and
  * bench.py's cpu_baseline / reference arm may load this library; the product path never does.
  *
- * Pinned against the reference itself: tests/test_oracle_kmeans.py runs oracle/_ref/centroid-merge
+ * Pinned against the reference itself: tests/test_oracle_golden.py runs oracle/_ref/centroid-merge
  * (the unmodified reference CLI) on the same snapshot files and requires byte-identical output.
  */
 #include <math.h>

@@ -14,8 +14,8 @@ GEMM-derived results are compared with tolerances, never bit-for-bit).
 
 Parity pins:
   * k-means merge and both centroid loops: byte-identical to the unmodified reference binary
-    oracle/_ref/centroid-merge on the same snapshot files (tests/test_oracle_kmeans.py), and
-    tests/golden/kmeans_cfg1.npz holds the reference binary's output for BASELINE config 1.
+    oracle/_ref/centroid-merge on the same snapshot files (tests/test_oracle_golden.py), and
+    tests/golden/kmeans_cfg1.npz holds the reference binary's output for the 2048 x 512, k = 8 merge case.
   * forward / cross-entropy / backward / AdamW / centroid / checkpoint files: against dumps of the
     unmodified reference objects run by oracle/ref_harness.cu on a B200, committed as
     tests/golden/ref_*.npz together with tests/golden/make_golden.py which made them.
@@ -289,7 +289,7 @@ class BaseConfig:
 
 
 #: projections that can carry a LoRA pair. The reference wires only the first four
-#: (src/adapter/adapter_model.cu:82-87); gate/up/down are the extension BASELINE configs 4-5 ask for.
+#: (src/adapter/adapter_model.cu:82-87); gate/up/down are an extension (the 1.5B and 7B benchmark configurations adapt all seven).
 ALL_TARGETS = ("q", "k", "v", "o", "gate", "up", "down")
 
 
@@ -612,7 +612,7 @@ def read_merged_file(path: str) -> np.ndarray:
 
 def cfg1_vectors(seed: int = 0, n_snap: int = 32, per_snap: int = 64, D: int = 512, n_centres: int = 12,
                  sigma: float = 0.1):
-    """BASELINE config 1 synthetic input: 12 Gaussian centres ~N(0,1), per-vector noise sigma=0.1,
+    """Synthetic merge input (the 32 x 64 snapshot case): 12 Gaussian centres ~N(0,1), per-vector noise sigma=0.1,
     per-vector gradient mass lognormal(0,1). Returns (vectors [N,D] f32, mass [N] f32)."""
     rng = np.random.default_rng(seed)
     centres = rng.standard_normal((n_centres, D)).astype(F32)

@@ -155,6 +155,18 @@ int ta_device_status(ta_ctx* ctx, int* status) {
 
 long ta_launch_count(const ta_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+int ta_ctx_set_gemm_tuning(ta_ctx* ctx, int tile_n, int tile_m_halves, int cta_pair) {
+    if (!ctx) return TA_ERR_INVALID;
+    const bool none = tile_n == 0 && tile_m_halves == 0;
+    const bool ok = (tile_m_halves == 1 || tile_m_halves == 2) &&
+                    (tile_n == 64 || tile_n == 128 || tile_n == 224 || tile_n == 256) && (tile_m_halves == 1 || tile_n >= 224);
+    if (!none && !ok) return ta::fail(ctx, TA_ERR_INVALID, "gemm tuning: tile_n in {64,128,224,256}, halves 1 or 2 (2 needs tile_n >= 224)");
+    ctx->gemm_force_bn = tile_n;
+    ctx->gemm_force_mh = tile_m_halves;
+    ctx->gemm_pair = cta_pair != 0;
+    return TA_OK;
+}
+
 int ta_profile_enable(ta_ctx* ctx, int on) {
     if (!ctx) return TA_ERR_INVALID;
     ctx->profiling = on != 0;

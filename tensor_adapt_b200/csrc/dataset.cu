@@ -104,9 +104,10 @@ using namespace ta;
 
 extern "C" {
 
-int ta_mask_targets_device(ta_ctx* ctx, const int* input_ids, int* target_ids, int B, int T, cudaStream_t stream) {
+int ta_mask_targets_device(ta_ctx* ctx, const int* input_ids, int* target_ids, int B, int T, void* stream_) {
     if (!ctx || !input_ids || !target_ids || B < 0 || T <= 0) return TA_ERR_INVALID;
     if (B == 0) return TA_OK;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     mask_targets_kernel<<<B, kMaskThreads, 0, stream>>>(input_ids, target_ids, T);
     TA_LAUNCH_CHECK(ctx, "mask_targets_kernel");
     return TA_OK;
@@ -189,7 +190,8 @@ int ta_dataset_seek(ta_dataset* ds, long position, long tokens_consumed) {
 }
 
 int ta_dataset_next_batch(ta_dataset* ds, int B, int T, int first_seq, int n_seq, int* ids_dev, int* targets_dev, int mask,
-                          cudaStream_t stream) {
+                          void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!ds || B <= 0 || T <= 0 || first_seq < 0 || n_seq < 0 || first_seq + n_seq > B || (n_seq && (!ids_dev || !targets_dev)))
         return TA_ERR_INVALID;
     if (n_seq) {

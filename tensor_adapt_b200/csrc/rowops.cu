@@ -414,10 +414,11 @@ __global__ void f32_to_bf16_tail(const float* src, __nv_bfloat16* dst, long from
 // re-reads the row (an L2 hit: a row is ~300 KB) and writes dlogits = (softmax - onehot) * inv_count,
 // which may alias `logits`.  Targets < 0 contribute loss = logsumexp and gradient softmax*inv_count,
 // as the reference kernel does.
-__global__ void __launch_bounds__(1024) cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits,
+// `logits` and `dlogits` carry no __restrict__: the in-place call passes the same buffer for both.
+__global__ void __launch_bounds__(1024) cross_entropy_kernel(const __nv_bfloat16* logits,
                                                              const int* __restrict__ targets,
                                                              float* __restrict__ loss,
-                                                             __nv_bfloat16* __restrict__ dlogits, int V,
+                                                             __nv_bfloat16* dlogits, int V,
                                                              float inv_count) {
     __shared__ float red_m[32], red_s[32];
     __shared__ float s_lse;

@@ -12,7 +12,6 @@
 
 #include <algorithm>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 
 #include "ptx.cuh"
@@ -546,7 +545,8 @@ struct TileChoice { int bn, mh; };
 // Tile shape by a small cost model: waves of tiles over the SMs x (main-loop clocks / delivery
 // efficiency of the shape + non-overlapped per-tile clocks).  The efficiencies are measured ratios of
 // achieved to peak tensor throughput of each shape on large problems.
-TileChoice pick_tile(int M, int N, double ksum, bool any_a_mn, int sms) {
+TileChoice pick_tile(const ta_ctx* ctx, int M, int N, double ksum, bool any_a_mn) {
+    const int sms = ctx->sm_count;
     if (N <= 16) return {16, 1};
     if (N <= 32) return {32, 1};
     if (N <= 64) return {64, 1};
@@ -554,12 +554,9 @@ TileChoice pick_tile(int M, int N, double ksum, bool any_a_mn, int sms) {
     // eff = measured (tile FLOPs / 8192 per clock) / (clocks per tile) on 16384-row problems, K >= 3584
     static const Cand cands[] = {{256, 2, 0.645, 2600}, {224, 2, 0.63, 2400}, {256, 1, 0.53, 400},
                                  {224, 1, 0.50, 400},   {128, 1, 0.31, 300},  {64, 1, 0.18, 250}};
-    if (const char* f = std::getenv("TA_GEMM_TILE")) {   // tuning knob: "BN,MH" forces one tile shape
-        int bn = 0, mh = 0;
-        if (std::sscanf(f, "%d,%d", &bn, &mh) == 2 && (mh == 1 || (mh == 2 && !any_a_mn && M >= 256)) &&
-            (bn == 64 || bn == 128 || bn == 224 || bn == 256) && (mh == 1 || bn >= 224))
-            return {bn, mh};
-    }
+    // experiment override (ta_ctx_set_gemm_tuning), honoured where the shape allows it
+    if (ctx->gemm_force_bn && (ctx->gemm_force_mh == 1 || (!any_a_mn && M >= 256)))
+        return {ctx->gemm_force_bn, ctx->gemm_force_mh};
     TileChoice best{64, 1};
     double best_t = 1e300;
     for (const Cand& c : cands) {
@@ -626,13 +623,11 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     double ksum_all = 0;
     bool any_a_mn = false;
     for (int s = 0; s < nseg; s++) { ksum_all += segs[s].K; any_a_mn = any_a_mn || segs[s].a_mn; }
-    const TileChoice tcfg = out.split_k > 1 ? TileChoice{pick_bn(N), 1} : pick_tile(M, N, ksum_all, any_a_mn, ctx->sm_count);
+    const TileChoice tcfg = out.split_k > 1 ? TileChoice{pick_bn(N), 1} : pick_tile(ctx, M, N, ksum_all, any_a_mn);
     const int bn = tcfg.bn, tile_m = 128 * tcfg.mh;
     // CTA-pair kernel (512 x 256 tiles over two SMs): same A boxes as the 256-row kernel, half-width B boxes.
-    // Opt-in (TA_GEMM_PAIR=1): measured 3-7 % slower than the single-CTA 256-row kernel on the 7B shapes.
-    const char* pair_env = std::getenv("TA_GEMM_PAIR");
-    const bool pair_enabled = pair_env && pair_env[0] == '1';
-    const bool use_pair = pair_enabled && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
+    // Opt-in (ta_ctx_set_gemm_tuning): measured 3-7 % slower than the single-CTA 256-row kernel on the 7B shapes.
+    const bool use_pair = ctx->gemm_pair && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
     SegGemmParams p;
     std::memset(&p, 0, sizeof(p));
     for (int s = 0; s < nseg; s++) {

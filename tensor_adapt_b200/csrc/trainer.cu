@@ -568,7 +568,11 @@ int ta_trainer_forward_backward(ta_trainer* t, const int* tokens, const int* tar
                                 int host_inputs) {
     if (!t || !tokens || !targets || B <= 0 || T <= 0) return fail(t ? t->ctx : nullptr, TA_ERR_INVALID, "forward_backward: bad argument");
     if (T != t->T) return fail(t->ctx, TA_ERR_INVALID, "forward_backward: T differs from the trainer's seq_len");
-    if (global_tokens <= 0) global_tokens = long(B) * T;
+    // Tokens are counted once per optimiser step: a caller that names the step's global token count (a
+    // data-parallel rank, or several accumulating calls) has exactly that many consumed by the step, as
+    // AdaptTrainer counts batch_size * seq_len per step (src/trainer/adapt_trainer.cu:255-256).
+    if (global_tokens > 0) t->pending_tokens = global_tokens;
+    else { global_tokens = long(B) * T; t->pending_tokens += global_tokens; }
     const float inv = 1.f / float(global_tokens);
     const cudaMemcpyKind kind = host_inputs ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
     for (int b0 = 0; b0 < B; b0 += t->micro_B) {
@@ -578,7 +582,6 @@ int ta_trainer_forward_backward(ta_trainer* t, const int* tokens, const int* tar
         TA_CUDA(t->ctx, cudaMemcpyAsync(t->tgt, targets + size_t(b0) * T, bytes, kind, t->stream));
         if (int rc = run_micro(t, Bm, T, inv)) return rc;
     }
-    t->tokens_seen += long(B) * T;
     return TA_OK;
 }
 
@@ -593,6 +596,8 @@ int ta_trainer_optimizer_step(ta_trainer* t, float lr, long total_steps, ta_step
     TA_CUDA(t->ctx, cudaMemcpyAsync(t->h_stats, t->stats, 4 * sizeof(float), cudaMemcpyDeviceToHost, t->stream));
     TA_CUDA(t->ctx, cudaStreamSynchronize(t->stream));
     t->step_count++;
+    t->tokens_seen += t->pending_tokens;
+    t->pending_tokens = 0;
     if (out) {
         out->step = t->step_count;
         out->tokens_consumed = t->tokens_seen;

@@ -80,6 +80,7 @@ struct ta_trainer {
     float* h_stats = nullptr;
     // bookkeeping
     long step_count = 0, tokens_seen = 0;
+    long pending_tokens = 0;  // tokens of the optimiser step in progress, added to tokens_seen when it completes
     std::string arch_name = "qwen2", base_sha;
     std::vector<std::vector<float>> snapshots;   // chronological, as CentroidAccumulator keeps them
 

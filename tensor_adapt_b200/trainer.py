@@ -45,7 +45,7 @@ class StepMetrics(ctypes.Structure):
 
 
 QWEN2 = {
-    # BASELINE configs 3-5 (shapes of Qwen2-0.5B / 1.5B / 7B)
+    # shapes of Qwen2-0.5B / 1.5B / 7B
     "qwen2-0.5b": ModelConfig(151936, 896, 24, 14, 2, 64, 4864, 1e-6, 1e6, 1),
     "qwen2-1.5b": ModelConfig(151936, 1536, 28, 12, 2, 128, 8960, 1e-6, 1e6, 1),
     "qwen2-7b": ModelConfig(152064, 3584, 28, 28, 4, 128, 18944, 1e-6, 1e6, 0),

@@ -32,6 +32,7 @@ def main(out_path):
         m = dp.step(toks[s], tgts[s], B, lr=2e-4)
         out[f"gnorm{s}"] = np.float32(m.grad_norm_raw)
         out[f"loss{s}"] = np.float32(m.loss)
+        out[f"tokens{s}"] = np.int64(m.tokens_consumed)
         out[f"master{s}"] = tr.download("lora.master")
     out["grad_last"] = tr.download("lora.grad")
     out["centroid"], out["centroid_w"] = dp.write_snapshot(2)

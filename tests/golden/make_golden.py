@@ -10,11 +10,11 @@ Run on a machine with a B200 and the compiled reference (oracle/_ref, built by `
                       before clipping, grad norm, masters after each step, both centroid snapshots)
   ref_ckpt_tiny/      the reference's own AdapterWriter output for the final masters of that run
                       (adapter.safetensors, adapter.json, train_state.json)
-  ref_op_cfg2.npz     BASELINE config 2 single LoRA-linear op (4096 x 896 -> 896, r16, alpha 32):
+  ref_op_cfg2.npz     single LoRA-linear op (4096 x 896 -> 896, r16, alpha 32):
                       seed + reference outputs gA, gB in full and every 32nd row of y, dX (BF16 bits)
   ref_load_tiny.json  BaseLoader::load on the seeded model directory of tests/refcase.py hf_case(): the
                       derived config, base_sha and the SHA-256 of every loaded tensor's BF16 bytes
-  kmeans_cfg1.npz     BASELINE config 1 k-means through the reference CLI oracle/_ref/centroid-merge:
+  kmeans_cfg1.npz     32 x 64 snapshot k-means through the reference CLI oracle/_ref/centroid-merge:
                       vector order as the reference enumerated it + merged centres (runs without a GPU)
 """
 import os

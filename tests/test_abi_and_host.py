@@ -31,6 +31,23 @@ def test_library_exports_every_declared_symbol():
     assert not undeclared, f"bound in _lib.py but not declared in the header: {undeclared}"
 
 
+@pytest.mark.parametrize("compiler,flags", [("gcc", ["-std=c99", "-x", "c"]), ("g++", ["-std=c++17", "-x", "c++"])])
+def test_header_compiles_as_plain_c_and_cpp(compiler, flags, tmp_path):
+    """The boundary is a C ABI: the header must stand alone (no CUDA headers) for a C99 and a C++ compiler,
+    and a translation unit that takes the address of an entry point must compile against it."""
+    import shutil
+    import subprocess
+    if not shutil.which(compiler):
+        pytest.skip(f"{compiler} not installed")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "tensor_adapt_b200.h"\n'
+                   'int probe(void) { ta_ctx* c = 0; int s = 0; return ta_device_status(c, &s) + TA_ERR_INVALID; }\n'
+                   'int (*p_batch)(ta_dataset*, int, int, int, int, int*, int*, int, void*) = ta_dataset_next_batch;\n')
+    r = subprocess.run([compiler, *flags, "-Wall", "-Werror", "-pedantic", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), str(src)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_every_entry_point_cites_the_reference():
     txt = open(os.path.join(ROOT, "include", "tensor_adapt_b200.h")).read()
     # each declaration block is preceded by a comment naming a reference file:line
@@ -95,3 +112,22 @@ def test_shard_ranges():
     tok = np.arange(8 * 4); tgt = tok + 1
     a, b, n = shard_batch(tok, tgt, 8, 4, 1, 2)
     assert n == 4 and a[0] == 16 and b[-1] == 32
+
+
+def test_reference_arm_of_bench_does_not_load_the_product_library():
+    """`bench.py --impl reference` must time the reference alone: the process prints its one JSON line (a
+    measurement on a GPU box, an `unavailable` line elsewhere) without ever importing the CUDA package."""
+    import json
+    import subprocess
+    import sys
+    code = ("import sys, runpy\n"
+            f"sys.argv = ['bench.py', '--impl', 'reference', '--steps', '1', '--warmup', '0', '--config', 'qwen2-0.5b']\n"
+            f"runpy.run_path({os.path.join(ROOT, 'bench.py')!r}, run_name='__main__')\n"
+            "assert not [m for m in sys.modules if m.startswith('tensor_adapt_b200')], 'product package imported'\n")
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("on a GPU box this would run the reference's full step; the GPU tests cover it")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["impl"] == "reference" and ("unavailable" in line or line["value"] > 0)

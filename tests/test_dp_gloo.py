@@ -73,6 +73,8 @@ class _FakeTrainer:
         self.t = {"lora.grad": torch.zeros(6), "step.stats": torch.zeros(4), "centroid.acc": torch.zeros(3),
                   "centroid.weight": torch.zeros(1)}
         self.written = []
+        self.tokens_consumed = 0
+        self.pending = 0
 
     def torch_view(self, name):
         return self.t[name]
@@ -82,11 +84,13 @@ class _FakeTrainer:
 
     def forward_backward(self, tok, tgt, b_local, global_tokens=0):
         self.t["lora.grad"] += float(np.sum(tok)) / global_tokens
+        self.pending = global_tokens          # the library counts the step's GLOBAL tokens once, on every rank
         self.t["step.stats"][2] += float(np.sum(tgt)); self.t["step.stats"][3] += len(tgt)
         self.t["centroid.acc"] += self.rank + 1.0; self.t["centroid.weight"] += 2.0
 
     def optimizer_step(self, lr, total_steps):
         s = self.t["step.stats"]
+        self.tokens_consumed += self.pending; self.pending = 0
         return float(s[2] / s[3]), self.t["lora.grad"].clone()
 
     def write_snapshot(self, step, mode=0):
@@ -105,7 +109,7 @@ def _dp_step_main(rank, world, port, out_dir):
     loss, grad = dp.step(toks, tgts, global_batch=4)
     cen, w = dp.write_snapshot(1)
     np.savez(os.path.join(out_dir, f"r{rank}.npz"), loss=loss, grad=grad.numpy(), cen=cen, w=w,
-             local_w=tr.t["centroid.weight"].numpy(), wrote=np.array([d is not None for d in tr.written]),
+             local_w=tr.t["centroid.weight"].numpy(), tokens=np.int64(tr.tokens_consumed), wrote=np.array([d is not None for d in tr.written]),
              out_dir_kept=np.array(tr.output_dir == out_dir))
     dist.barrier()
     dist.destroy_process_group()
@@ -121,4 +125,5 @@ def test_data_parallel_step_reduces_grads_loss_and_snapshot(tmp_path):
         np.testing.assert_allclose(z["cen"], np.full(3, 3.0 / 4.0))                  # (1 + 2) / (2 + 2)
         assert float(z["w"]) == 4.0 and float(z["local_w"][0]) == 2.0                # local sums restored
         assert bool(z["out_dir_kept"])
+        assert int(z["tokens"]) == 16                                               # global batch 4 x seq_len 4, not the shard
     assert z0["wrote"].tolist() == [True] and z1["wrote"].tolist() == [False]        # only rank 0 gets a path

@@ -65,7 +65,7 @@ def test_flash_attention_fwd_bwd(ctx, B, T, Hq, Hkv, hd):
 
 
 def test_flash_attention_long_sequence_properties(ctx):
-    """T = 4096 (BASELINE config 5's sequence length), too large for the O(T^2) oracle: check
+    """T = 4096 (the 7B configuration's sequence length), too large for the O(T^2) oracle: check
     size-independent properties instead - row 0 attends only to itself (out[0] == V[0]); a constant V
     is reproduced exactly; and the first 256 rows equal a T=256 run of the same prefix (causality)."""
     B, T, Hq, Hkv, hd = 1, 4096, 4, 2, 128

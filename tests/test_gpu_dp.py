@@ -37,6 +37,7 @@ def test_two_gpu_step_equals_single_gpu(ctx, tmp_path):
         m = tr.step(toks[s], tgts[s], B, lr=2e-4)
         assert abs(m.grad_norm_raw - float(z[f"gnorm{s}"])) <= 1e-4 * m.grad_norm_raw
         assert abs(m.loss - float(z[f"loss{s}"])) <= 1e-5 * abs(m.loss)          # global-batch mean on every rank
+        assert int(z[f"tokens{s}"]) == m.tokens_consumed == (s + 1) * B * T       # a rank counts the GLOBAL batch per step
         # Adam's sign-like first steps can flip on near-zero gradients: allow a few 2*lr outliers
         d = np.abs(tr.download("lora.master") - z[f"master{s}"])
         assert np.mean(d > 1e-6) < 1e-3 and d.max() <= 2.2 * 2e-4 * (s + 1)

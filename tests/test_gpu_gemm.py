@@ -97,6 +97,7 @@ def test_gemm_tokens_f32(ctx, M, N, K, transpose):
     C2 = C0.clone()
     ctx.call("ta_gemm_tokens_f32", M, N, K, 2.0, ptr(A), M, ptr(B), N, ptr(C2), shape[1], 1, int(transpose), stream_ptr())
     torch.cuda.synchronize()
+    ctx.call("ta_ctx_set_gemm_tuning", 0, 0, 0)
     assert torch.equal(C, C2)
 
 
@@ -110,11 +111,10 @@ def test_gemm_rejects_bad_arguments(ctx):
 
 @pytest.mark.parametrize("M,N,K,b_layout,extras", [(512, 256, 64, 0, False), (1064, 776, 520, 0, False), (1064, 776, 520, 1, False),
                                                      (2048, 1024, 1000, 0, True), (1536, 3584, 1024, 1, True)])
-def test_cta_pair_kernel_matches_fp32_reference(ctx, monkeypatch, M, N, K, b_layout, extras):
+def test_cta_pair_kernel_matches_fp32_reference(ctx, M, N, K, b_layout, extras):
     """The opt-in CTA-pair kernel (tcgen05 cta_group::2, 512 x 256 tiles over two SMs) against an FP32
     torch product: K-major and MN-major B, ragged M / N / K, bias and residual."""
-    monkeypatch.setenv("TA_GEMM_PAIR", "1")
-    monkeypatch.setenv("TA_GEMM_TILE", "256,2")
+    ctx.call("ta_ctx_set_gemm_tuning", 256, 2, 1)
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     A = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
     B = (torch.randn((K, N) if b_layout else (N, K), device="cuda", generator=g) * 0.05).to(torch.bfloat16)
@@ -124,15 +124,16 @@ def test_cta_pair_kernel_matches_fp32_reference(ctx, monkeypatch, M, N, K, b_lay
     ctx.call("ta_gemm_bf16", M, N, K, 1.0, ptr(A), K, 0, ptr(B), B.shape[1], b_layout, ptr(bias) if extras else None,
              ptr(res) if extras else None, ptr(C), N, stream_ptr())
     torch.cuda.synchronize()
+    ctx.call("ta_ctx_set_gemm_tuning", 256, 2, 0)
     ctx.check_device()
     ref = A.float() @ (B.float() if b_layout else B.float().t())
     if extras:
         ref = ref + bias.float() + res.float()
     assert (C.float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max() + 1e-3
     # and it is the same result as the default kernel, bit for bit (same accumulation order per output element)
-    monkeypatch.delenv("TA_GEMM_PAIR")
     C2 = torch.zeros_like(C)
     ctx.call("ta_gemm_bf16", M, N, K, 1.0, ptr(A), K, 0, ptr(B), B.shape[1], b_layout, ptr(bias) if extras else None,
              ptr(res) if extras else None, ptr(C2), N, stream_ptr())
     torch.cuda.synchronize()
+    ctx.call("ta_ctx_set_gemm_tuning", 0, 0, 0)
     assert torch.equal(C, C2)

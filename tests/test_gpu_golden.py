@@ -1,7 +1,7 @@
 """CUDA path (through the C ABI) against the committed golden fixtures, i.e. outputs of the unmodified
 reference (tests/golden/, made by tests/golden/make_golden.py).  Needs no reference binary at run time.
 
-Bars: files and k-means bit-exact; BASELINE config 2 (single LoRA-linear op) at the stated tolerances
+Bars: files and k-means bit-exact; the single LoRA-linear op (4096 x 896 -> 896, r16) at the stated tolerances
 (gradients cosine >= 0.999 and max-rel <= 2e-2, BF16 outputs max-rel <= 2e-2); the 2-layer training step at
 the measured BF16 noise floor documented in tests/test_gpu_trainer.py."""
 import os
@@ -101,7 +101,7 @@ def test_checkpoint_files_byte_identical_to_reference(ctx, tmp_path):
 
 
 def test_centroid_merge_dir_vs_reference_golden(ctx, tmp_path):
-    """BASELINE config 1 through the file-level entry point (CentroidMerge::run): the reference CLI's
+    """The 32 x 64 snapshot merge case through the file-level entry point (CentroidMerge::run): the reference CLI's
     merged centres are reproduced bit for bit when the vectors are enumerated in the same order."""
     from tensor_adapt_b200.trainer import centroid_merge
     z = np.load(os.path.join(GOLD, "kmeans_cfg1.npz"))

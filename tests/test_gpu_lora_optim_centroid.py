@@ -1,4 +1,4 @@
-"""LoRA linear fwd/bwd (BASELINE config 2 and small ragged cases), the flat-arena optimiser, the
+"""LoRA linear fwd/bwd (the 4096 x 896 -> 896 rank-16 single-op case and small ragged cases), the flat-arena optimiser, the
 device centroid accumulator and the device k-means, each through the C ABI against the oracle.
 
 Tolerances (config 2's, from the north star): LoRA gradients cosine >= 0.999 and
@@ -148,7 +148,7 @@ def test_centroid_accumulate(ctx, BT, D, mode):
 @pytest.mark.parametrize("N,D,k,seed", [(2048, 512, 8, 0), (32, 896, 16, 1), (5, 64, 16, 2), (300, 40, 7, 3)])
 def test_kmeans_merge_bit_exact(ctx, N, D, k, seed):
     if (N, D) == (2048, 512):
-        vec, _ = o.cfg1_vectors(seed)           # BASELINE config 1
+        vec, _ = o.cfg1_vectors(seed)           # the 32 x 64 snapshot merge case
     else:
         rng = np.random.default_rng(seed)
         vec = rng.standard_normal((N, D)).astype(np.float32)

@@ -142,7 +142,7 @@ def test_kmeans_plusplus_ranking_extension_properties():
     """No reference code exists for the seeded k-means++ / mass-ranked merge: the oracle's restatement is
     checked through properties - deterministic per seed, distinct start vectors, every label used,
     clusters in descending gradient mass, masses summing to the total, and on well-separated data
-    (BASELINE config 1: 12 centres, sigma 0.1) every cluster is pure."""
+    (12 centres, sigma 0.1) every cluster is pure."""
     vec, mass = o.cfg1_vectors(0)
     c1, a1, it1, tot1, idx1 = o.kmeans_merge_ex(vec, mass, 12, seed=3)
     c2, a2, it2, tot2, idx2 = o.kmeans_merge_ex(vec, mass, 12, seed=3)
