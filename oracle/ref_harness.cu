@@ -92,15 +92,24 @@ static void dump_tensor(const std::string& p, const Tensor& t) {
     dump(p, h.data(), h.size());
 }
 
-// Deterministic device fill for the timing mode (no parity meaning): N(0, std) in bf16.
+// Deterministic device fill, bit-identical to the package's ta_trainer_init_random (seed 0): approximately
+// normal N(0, std) BF16 values as the centred sum of twelve 16-bit hash fields, scaled with single
+// correctly-rounded operations so that this file's --use_fast_math build produces the same bits.  Lets both
+// implementations start from identical multi-gigabyte weights without writing them to disk.
+__device__ static unsigned long long k_mix64(unsigned long long z) {
+    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull; z ^= z >> 27; z *= 0x94D049BB133111EBull; z ^= z >> 31;
+    return z;
+}
 __global__ void k_fill_normal(__nv_bfloat16* p, std::size_t n, float stdv, unsigned seed) {
     std::size_t i = blockIdx.x * (std::size_t)blockDim.x + threadIdx.x;
     if (i >= n) return;
-    unsigned long long z = (i + 1) * 0x9E3779B97F4A7C15ull + seed * 0xD1B54A32D192ED03ull;
-    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull; z ^= z >> 27; z *= 0x94D049BB133111EBull; z ^= z >> 31;
-    float u1 = ((unsigned)(z >> 40) + 1.0f) / 16777217.0f;
-    float u2 = ((unsigned)(z & 0xFFFFFF)) / 16777216.0f;
-    p[i] = __float2bfloat16(stdv * sqrtf(-2.f * logf(u1)) * cosf(6.2831853f * u2));
+    const float c = __fmul_rn(stdv, 1.52587890625e-05f);
+    const unsigned long long x = (unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull + (unsigned long long)seed * 0xD1B54A32D192ED03ull;
+    const unsigned long long z[3] = {k_mix64(x), k_mix64(x ^ 0xA5A5A5A5A5A5A5A5ull), k_mix64(x + 0x632BE59BD9B4E019ull)};
+    int sum = 0;
+    for (int k = 0; k < 3; k++)
+        sum += int(z[k] & 0xFFFF) + int((z[k] >> 16) & 0xFFFF) + int((z[k] >> 32) & 0xFFFF) + int(z[k] >> 48);
+    p[i] = __float2bfloat16_rn(__fmul_rn(__int2float_rn(sum - 6 * 65535), c));
 }
 __global__ void k_fill_const(__nv_bfloat16* p, std::size_t n, float v) {
     std::size_t i = blockIdx.x * (std::size_t)blockDim.x + threadIdx.x;

@@ -29,12 +29,20 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
     z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull; z ^= z >> 27; z *= 0x94D049BB133111EBull; z ^= z >> 31;
     return z;
 }
+// Approximately normal N(0, stdv) BF16 values from an integer hash: the centred sum of twelve 16-bit fields of
+// three 64-bit hashes (variance 65536^2 - 1), scaled with single correctly-rounded operations only, so any
+// compiler setting (fast-math included) produces the same bits - the parity harness that drives the reference
+// fills its weights with the same function.
 __global__ void fill_normal_kernel(bf16* p, long n, float stdv, unsigned long long seed) {
+    const float c = __fmul_rn(stdv, 1.52587890625e-05f);   // stdv / 65536, exact
     for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n; i += long(gridDim.x) * blockDim.x) {
-        const unsigned long long z = mix64((i + 1) * 0x9E3779B97F4A7C15ull + seed * 0xD1B54A32D192ED03ull);
-        const float u1 = (float(unsigned(z >> 40)) + 1.0f) / 16777217.0f;
-        const float u2 = float(unsigned(z & 0xFFFFFFu)) / 16777216.0f;
-        p[i] = __float2bfloat16(stdv * sqrtf(-2.f * logf(u1)) * cosf(6.283185307f * u2));
+        const unsigned long long x = (unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull + seed * 0xD1B54A32D192ED03ull;
+        const unsigned long long z[3] = {mix64(x), mix64(x ^ 0xA5A5A5A5A5A5A5A5ull), mix64(x + 0x632BE59BD9B4E019ull)};
+        int sum = 0;
+#pragma unroll
+        for (int k = 0; k < 3; k++)
+            sum += int(z[k] & 0xFFFF) + int((z[k] >> 16) & 0xFFFF) + int((z[k] >> 32) & 0xFFFF) + int(z[k] >> 48);
+        p[i] = __float2bfloat16_rn(__fmul_rn(__int2float_rn(sum - 6 * 65535), c));
     }
 }
 __global__ void fill_const_kernel(bf16* p, long n, float v) {

@@ -176,6 +176,15 @@ class AdaptTrainer:
         assert dt == 0 and r == 1
         return torch.as_tensor(_CudaView(p, c, "<f4"), device=f"cuda:{self.ctx.device}")
 
+    def torch_tensor(self, name: str):
+        """Zero-copy 2-D torch view [rows, cols] (row pitch respected) of any named tensor, FP32 or BF16."""
+        import torch
+        p, r, c, pitch, dt = self.tensor(name)
+        flat = torch.as_tensor(_CudaView(p, r * pitch, "<f4" if dt == 0 else "<i2"), device=f"cuda:{self.ctx.device}")
+        if dt == 1:
+            flat = flat.view(torch.bfloat16)
+        return flat.view(r, pitch)[:, :c]
+
     # ── model state ─────────────────────────────────────────────────────────
     def init_random(self, seed: int = 0, std: float = 0.02) -> None:
         self._call("ta_trainer_init_random", seed, std)

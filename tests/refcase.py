@@ -31,6 +31,8 @@ def make_case(cfg, B, T, rank, targets=("q", "k", "v", "o"), seed=0, steps=1, st
 
 
 def write_case_dir(d, cfg, base, adapter, toks, tgts, B, T, rank, alpha, **extra):
+    """`base=None` leaves the weight files out: ref_harness then fills the base on the device with the same
+    integer-hash generator as ta_trainer_init_random(seed 0), bit for bit."""
     os.makedirs(d, exist_ok=True)
     kv = dict(vocab=cfg.vocab, hidden=cfg.hidden, layers=cfg.layers, hq=cfg.hq, hkv=cfg.hkv, hd=cfg.hd, inter=cfg.inter,
               eps=cfg.eps, theta=cfg.theta, tie=int(cfg.tie), rank=rank, alpha=alpha, B=B, T=T, steps=len(toks))
@@ -39,12 +41,14 @@ def write_case_dir(d, cfg, base, adapter, toks, tgts, B, T, rank, alpha, **extra
         for k, v in kv.items():
             f.write(f"{k} {v}\n")
     w = lambda name, a: o.bf16_bits(a).astype("<u2").tofile(os.path.join(d, name + ".bin"))
-    w("embed", base["embed"]); w("final_norm", base["final_norm"])
-    if not cfg.tie:
-        w("lm_head", base["lm_head"])
-    for l, lw in enumerate(base["layers"]):
-        for k in LAYER_KEYS:
-            w(f"l{l}_{k}", lw[k])
+    if base is not None:
+        w("embed", base["embed"]); w("final_norm", base["final_norm"])
+        if not cfg.tie:
+            w("lm_head", base["lm_head"])
+    for l in range(cfg.layers):
+        if base is not None:
+            for k in LAYER_KEYS:
+                w(f"l{l}_{k}", base["layers"][l][k])
         for t, lp in adapter[l].items():
             lp.A_f32.astype("<f4").tofile(os.path.join(d, f"l{l}_lora_{t}_A.bin"))
             lp.B_f32.astype("<f4").tofile(os.path.join(d, f"l{l}_lora_{t}_B.bin"))
