@@ -147,14 +147,17 @@ int ta_gemm_tokens_f32_static(ta_ctx* ctx, int M, int N, int K, float alpha, con
  *     y[BT,out] = x.W^T (+ bias) + scale*(x.A^T).B^T (+ residual)
  * x [BT,in], W [out,in], A [rank,in], B [out,rank] BF16 (the working copies). A/B may be NULL (no
  * adapter); rank must then be 0, otherwise a multiple of 16. residual (may alias y) fuses the
- * following ops::add_inplace of the residual stream (qwen2.cu:126,150). Uses context scratch. */
+ * following ops::add_inplace of the residual stream (qwen2.cu:126,150). W may be NULL: only the adapter
+ * delta is formed, y = residual + scale*(x.A^T).B^T, which with residual == y is
+ * AdapterModel::apply_lora_fwd on an existing projection output. Uses context scratch. */
 int ta_lora_linear_fwd(ta_ctx* ctx, const void* x, const void* W, const void* bias, const void* A, const void* B,
                        const void* residual, void* y, int BT, int in_dim, int out_dim, int rank, float scale,
                        void* stream);
 /* proj_bwd_x + AdapterModel::apply_lora_bwd (qwen2.cu:32-41; adapter_model.cu:131-220):
  *     dX[BT,in] = (accumulate_dx ? dX : 0) + dY.W + scale*(dY.B).A
  *     gA[rank,in] += scale*(dY.B)^T.x        gB[out,rank] += scale*dY^T.(x.A^T)        (FP32)
- * with h = x.A^T and dh = dY.B rounded to BF16 as in the reference. Uses context scratch (split-K
+ * with h = x.A^T and dh = dY.B rounded to BF16 as in the reference. W may be NULL (the dY.W term is
+ * left out: AdapterModel::apply_lora_bwd with accumulate_dx = 1). Uses context scratch (split-K
  * partials reduced in a fixed order, so results are bit-identical from run to run). */
 int ta_lora_linear_bwd(ta_ctx* ctx, const void* x, const void* dY, const void* W, const void* A, const void* B, void* dX,
                        int accumulate_dx, float* gA, float* gB, int BT, int in_dim, int out_dim, int rank, float scale,

@@ -35,23 +35,27 @@ extern "C" {
 int ta_lora_linear_fwd(ta_ctx* ctx, const void* x, const void* W, const void* bias, const void* A, const void* B,
                        const void* residual, void* y, int BT, int in_dim, int out_dim, int rank, float scale,
                        void* stream) {
-    if (!ctx || !x || !W || !y || BT <= 0 || in_dim <= 0 || out_dim <= 0)
+    if (!ctx || !x || !y || BT <= 0 || in_dim <= 0 || out_dim <= 0)
         return fail(ctx, TA_ERR_INVALID, "lora_linear_fwd: null argument or bad size");
     const bool lora = A && B && rank > 0;
+    if (!W && !lora) return fail(ctx, TA_ERR_INVALID, "lora_linear_fwd: neither a base weight nor an adapter");
     if (lora && rank % 16 != 0) return fail(ctx, TA_ERR_UNSUPPORTED, "lora_linear_fwd: rank must be a multiple of 16");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     GemmSegment seg[2];
-    seg[0].A = static_cast<const __nv_bfloat16*>(x); seg[0].lda = in_dim;
-    seg[0].B = static_cast<const __nv_bfloat16*>(W); seg[0].ldb = in_dim; seg[0].K = in_dim;
-    int nseg = 1;
+    int nseg = 0;
+    if (W) {   // W == NULL: the adapter delta alone (AdapterModel::apply_lora_fwd on an existing projection output)
+        seg[0].A = static_cast<const __nv_bfloat16*>(x); seg[0].lda = in_dim;
+        seg[0].B = static_cast<const __nv_bfloat16*>(W); seg[0].ldb = in_dim; seg[0].K = in_dim;
+        nseg = 1;
+    }
     if (lora) {
         void* ws = nullptr;
         if (int rc = get_workspace(ctx, lora_fwd_scratch_bytes(BT, rank), &ws)) return rc;
         LoraRef l; l.A = static_cast<const __nv_bfloat16*>(A); l.B = static_cast<const __nv_bfloat16*>(B); l.r = rank;
-        if (int rc = lora_down(ctx, s, seg[0].A, BT, in_dim, l, scale, static_cast<__nv_bfloat16*>(ws))) return rc;
-        seg[1].A = static_cast<const __nv_bfloat16*>(ws); seg[1].lda = rank;
-        seg[1].B = l.B; seg[1].ldb = rank; seg[1].K = rank;
-        nseg = 2;
+        if (int rc = lora_down(ctx, s, static_cast<const __nv_bfloat16*>(x), BT, in_dim, l, scale, static_cast<__nv_bfloat16*>(ws))) return rc;
+        GemmSegment& g = seg[nseg++];
+        g.A = static_cast<const __nv_bfloat16*>(ws); g.lda = rank;
+        g.B = l.B; g.ldb = rank; g.K = rank;
     }
     GemmOut o;
     o.C = y; o.ldc = out_dim;
@@ -63,17 +67,21 @@ int ta_lora_linear_fwd(ta_ctx* ctx, const void* x, const void* W, const void* bi
 int ta_lora_linear_bwd(ta_ctx* ctx, const void* x, const void* dY, const void* W, const void* A, const void* B, void* dX,
                        int accumulate_dx, float* gA, float* gB, int BT, int in_dim, int out_dim, int rank, float scale,
                        void* stream) {
-    if (!ctx || !dY || !W || !dX || BT <= 0 || in_dim <= 0 || out_dim <= 0)
+    if (!ctx || !dY || !dX || BT <= 0 || in_dim <= 0 || out_dim <= 0)
         return fail(ctx, TA_ERR_INVALID, "lora_linear_bwd: null argument or bad size");
     const bool lora = A && B && rank > 0;
+    if (!W && !lora) return fail(ctx, TA_ERR_INVALID, "lora_linear_bwd: neither a base weight nor an adapter");
     if (lora && (!x || !gA || !gB)) return fail(ctx, TA_ERR_INVALID, "lora_linear_bwd: x, gA and gB are required with LoRA");
     if (lora && rank % 16 != 0) return fail(ctx, TA_ERR_UNSUPPORTED, "lora_linear_bwd: rank must be a multiple of 16");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const __nv_bfloat16* dy = static_cast<const __nv_bfloat16*>(dY);
     GemmSegment seg[2];
-    seg[0].A = dy; seg[0].lda = out_dim;
-    seg[0].B = static_cast<const __nv_bfloat16*>(W); seg[0].ldb = in_dim; seg[0].b_mn = true; seg[0].K = out_dim;
-    int nseg = 1;
+    int nseg = 0;
+    if (W) {   // W == NULL: the adapter's share alone (AdapterModel::apply_lora_bwd)
+        seg[0].A = dy; seg[0].lda = out_dim;
+        seg[0].B = static_cast<const __nv_bfloat16*>(W); seg[0].ldb = in_dim; seg[0].b_mn = true; seg[0].K = out_dim;
+        nseg = 1;
+    }
     if (lora) {
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
         void* ws = nullptr;
@@ -103,8 +111,8 @@ int ta_lora_linear_bwd(ta_ctx* ctx, const void* x, const void* dY, const void* W
             o.split_k = tokens_gemm_splits(ctx, in_dim, rank, BT); o.split_ws = sk; o.split_ws_bytes = sk_bytes;
             if (int rc = seg_gemm(ctx, s, in_dim, rank, &g, 1, o)) return rc;
         }
-        seg[1].A = dh_s; seg[1].lda = rank; seg[1].B = l.A; seg[1].ldb = in_dim; seg[1].b_mn = true; seg[1].K = rank;
-        nseg = 2;
+        GemmSegment& g = seg[nseg++];
+        g.A = dh_s; g.lda = rank; g.B = l.A; g.ldb = in_dim; g.b_mn = true; g.K = rank;
     }
     GemmOut o;
     o.C = dX; o.ldc = in_dim;
