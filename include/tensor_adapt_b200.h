@@ -48,6 +48,12 @@ const char* ta_last_error(const ta_ctx* ctx);
 /* Synchronous read (and reset) of the device status word: TA_OK, or TA_ERR_DEVICE_TIMEOUT with
  * *status = the code of the wait that gave up.  The CUDA context stays usable either way. */
 int ta_device_status(ta_ctx* ctx, int* status);
+/* Self-test of the bounded device waits (no counterpart in the reference, whose kernels never wait on one
+ * another): a one-warp kernel waits limit_us microseconds on a barrier that nothing arrives at, gives up, records
+ * its status code and returns.  Afterwards ta_device_status() reports TA_ERR_DEVICE_TIMEOUT with *status = 106 and
+ * the context is usable as before.  *wait_returned_true receives 0 (the wait gave up), *abort_flag_seen 1 (the
+ * rest of the CTA saw the abort flag).  Synchronises the stream. */
+int ta_selftest_bounded_wait(ta_ctx* ctx, int limit_us, int* wait_returned_true, int* abort_flag_seen, void* stream);
 /* Kernels launched through this context so far. */
 long ta_launch_count(const ta_ctx* ctx);
 /* Experiment knob, no counterpart in the reference: force the GEMM tile (tile_n in {64,128,224,256},
@@ -124,9 +130,9 @@ int ta_gemm_bf16(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, l
  * transpose_out != 0 stores C^T (C is then [N][ldc]). */
 int ta_gemm_tokens_f32(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, long lda, const void* B, long ldb,
                        float* C, long ldc, int accumulate, int transpose_out, void* stream);
-/* The same product for callers that cannot allocate device memory (a CUDA-graph capture in progress,
- * a host application that owns all of device memory through its own pool, a plugin sandbox that forbids
- * cudaMalloc and the device-wide synchronisation it implies).  It has no counterpart in the reference,
+/* The same product for callers that cannot allocate device memory (a host application that owns all of
+ * device memory through its own pool, a plugin sandbox that forbids cudaMalloc and the device-wide
+ * synchronisation it implies).  It has no counterpart in the reference,
  * whose every op allocates its temporaries (src/adapter/adapter_model.cu:142-191).  Same arguments and
  * results as ta_gemm_tokens_f32, but the split-K partials live in a fixed array inside the library image
  * (TA_STATIC_SCRATCH_BYTES, held by every GPU that loads the library until exit) and the call performs no
@@ -135,8 +141,8 @@ int ta_gemm_tokens_f32(ta_ctx* ctx, int M, int N, int K, float alpha, const void
  *     TA_ERR_NOMEM and a message naming the sizes; use ta_gemm_tokens_f32 for those;
  *   - the context's device must be the current device; the FIRST call on a device resolves the array's
  *     device address (cudaGetSymbolAddress) - make that first call before any stream capture begins;
- *   - all calls share the one array: calls that may overlap on the GPU (different streams, or graphs
- *     replayed concurrently) race on it and must be serialised by the caller. */
+ *   - all calls share the one array: calls that may overlap on the GPU (different streams) race on it and
+ *     must be serialised by the caller. */
 #define TA_STATIC_SCRATCH_BYTES (8u << 20)
 int ta_gemm_tokens_f32_static(ta_ctx* ctx, int M, int N, int K, float alpha, const void* A, long lda, const void* B,
                               long ldb, float* C, long ldc, int accumulate, int transpose_out, void* stream);
@@ -251,7 +257,8 @@ typedef struct ta_adapter_config {    /* AdapterConfig, include/tensor/adapter/a
     float lr, grad_clip;
     int warmup_steps;
     float beta1, beta2, eps, weight_decay;
-    int centroid_modes;               /* bit 0: intended accumulator, bit 1: as-built accumulator */
+    int centroid_modes;               /* bit 0: intended accumulator, bit 1: as-built accumulator,
+                                         bit 2: per-layer bank (one intended accumulator per layer) */
 } ta_adapter_config;
 
 typedef struct ta_step_metrics {      /* StepMetrics, adapt_trainer.hpp:18-27 (wall-clock fields are the caller's) */
@@ -280,6 +287,7 @@ int ta_trainer_init_random(ta_trainer* tr, unsigned long long seed, float std);
  *   "l<i>.lora.<q|k|v|o|gate|up|down>.<A|B|gA|gB|mA|mB|vA|vB|A_bf16|B_bf16>"
  *   "lora.master" "lora.grad" "lora.m" "lora.v" "lora.working" (whole flat arrays)
  *   "centroid.acc" "centroid.weight" "centroid_asbuilt.acc" "centroid_asbuilt.weight"
+ *   "centroid_bank.acc" [layers, hidden] "centroid_bank.weight" [layers]
  *   "l<i>.cache.<x_normed|Q|K|V|attn_out|r_in|r_mid>" "cache.dx_attn_in" (last micro-batch, layer 0)
  * dtype: 0 = FP32, 1 = BF16. pitch is the row pitch in elements. */
 int ta_trainer_tensor(ta_trainer* tr, const char* name, void** dev_ptr, long* rows, long* cols, long* pitch, int* dtype);
@@ -309,6 +317,13 @@ int ta_trainer_step(ta_trainer* tr, const int* tokens, const int* targets, int B
  * reference's layout int32 D | D x f32 | f32 weight, and into centroid_out[D] / weight_out (host, may be
  * NULL). Returns TA_OK without writing when the weight is zero, as the reference does. */
 int ta_trainer_write_snapshot(ta_trainer* tr, int mode, const char* path, float* centroid_out, float* weight_out);
+/* Multi-vector snapshot ("bank"): one normalised centroid per layer (centroid_modes bit 2), written as the
+ * reference's snapshot record int32 D | D x f32 | f32 weight repeated per layer, so a one-layer bank is exactly a
+ * reference snapshot file and the reference's reader sees the first record of a longer one.  centroids_out
+ * [layers*D] / weights_out [layers] (host, may be NULL); *n_records = layers with non-zero weight.  The README's
+ * "bank of vectors per snapshot" (README.md:73-79) has no code in the reference: no counterpart.
+ * ta_centroid_merge_dir_ex clusters every record of every file. */
+int ta_trainer_write_snapshot_bank(ta_trainer* tr, const char* path, float* centroids_out, float* weights_out, int* n_records);
 /* AdapterWriter::save_checkpoint / save_final (src/checkpoint/adapter_writer.cpp:130-159): writes
  * adapter.safetensors (BF16 of the FP32 masters, flat shapes, reference tensor names), adapter.json
  * and, unless final != 0, train_state.json into `dir`, byte-compatible with the reference's files. */
@@ -386,8 +401,9 @@ void ta_kaiming_init_host(float* out, int in_dim, int rank, unsigned seed);
  * writes int32 k | int32 D | k*D f32 to out_path. *n_vectors / *passes (may be NULL) report what ran. */
 int ta_centroid_merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, int k, int* n_vectors, int* passes);
 /* The same over ta_kmeans_merge_ex: seeded k-means++ start and / or the bank ordered by gradient mass,
- * the mass of a snapshot being the trailing weight field of its file (README.md:73-79 "merged cluster
- * bank, gradient-ranked"); same output layout. No reference counterpart. */
+ * the mass of a snapshot being the trailing weight field of its record (README.md:73-79 "merged cluster
+ * bank, gradient-ranked"); files that hold several records (snapshot banks) contribute all of them, in file
+ * order; same output layout. No reference counterpart. */
 int ta_centroid_merge_dir_ex(ta_ctx* ctx, const char* dir, const char* out_path, int k, int init_mode, unsigned long long seed,
                              int rank_by_mass, int* n_vectors, int* passes);
 /* Host <-> device copies for callers without a CUDA runtime binding (synchronous). */

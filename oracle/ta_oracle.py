@@ -680,6 +680,40 @@ def kmeans_merge_ex(vectors: np.ndarray, mass: Optional[np.ndarray], k: int, see
     return centers[order], inv[assign], it, tot[order], idx
 
 
+# Multi-vector snapshot banks (extension, no reference code): a snapshot FILE may hold several vectors, written as
+# the reference's single-vector record (src/centroid/centroid_accumulator.cpp:81-86: int32 D | D x f32 | f32 weight)
+# repeated back to back.  A one-record file is exactly the reference's snapshot; the reference's own reader sees the
+# first record of a longer one.  The trainer's bank holds one gradient-weighted centroid per layer.
+
+def write_bank_file(path: str, vectors: np.ndarray, weights: np.ndarray) -> None:
+    with open(path, "wb") as f:
+        for v, w in zip(np.asarray(vectors, dtype="<f4"), np.asarray(weights, dtype="<f4")):
+            f.write(struct.pack("<i", len(v))); f.write(np.ascontiguousarray(v).tobytes()); f.write(struct.pack("<f", float(w)))
+
+
+def read_bank_file(path: str) -> Tuple[np.ndarray, np.ndarray]:
+    """All records of a snapshot file: (vectors [n, D], weights [n])."""
+    b = open(path, "rb").read()
+    vs, ws, off = [], [], 0
+    while off + 4 <= len(b):
+        D = struct.unpack_from("<i", b, off)[0]
+        if D <= 0 or off + 8 + 4 * D > len(b):
+            break
+        vs.append(np.frombuffer(b, dtype="<f4", count=D, offset=off + 4).copy())
+        ws.append(struct.unpack_from("<f", b, off + 4 + 4 * D)[0])
+        off += 8 + 4 * D
+    return np.array(vs, dtype=F32), np.array(ws, dtype=F32)
+
+
+def layer_bank(hidden_per_layer, grad_per_layer) -> Tuple[np.ndarray, np.ndarray]:
+    """One documented-formula centroid per layer: (acc_l / weight_l [L, D], weight_l [L])."""
+    cs, ws = [], []
+    for h, g in zip(hidden_per_layer, grad_per_layer):
+        a = CentroidAccumulator(h.shape[1]); a.accumulate(h, g, "intended")
+        cs.append((a.acc / a.weight[0]).astype(F32)); ws.append(a.weight[0])
+    return np.array(cs, dtype=F32), np.array(ws, dtype=F32)
+
+
 # ───────────────────────────── checkpoint files ─────────────────────────────
 
 TARGET_NAMES = {"q": "self_attn.q_proj", "k": "self_attn.k_proj", "v": "self_attn.v_proj",

@@ -46,6 +46,7 @@ _PROTOS = {
     "ta_last_error": (c_char_p, [P]),
     "ta_device_status": (c_int, [P, POINTER(c_int)]),
     "ta_launch_count": (c_long, [P]),
+    "ta_selftest_bounded_wait": (c_int, [P, c_int, POINTER(c_int), POINTER(c_int), P]),
     "ta_ctx_set_gemm_tuning": (c_int, [P, c_int, c_int, c_int]),
     "ta_profile_enable": (c_int, [P, c_int]),
     "ta_profile_read": (c_int, [P, c_int, POINTER(c_long), POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
@@ -84,6 +85,7 @@ _PROTOS = {
     "ta_trainer_optimizer_step": (c_int, [P, c_float, c_long, P]),
     "ta_trainer_step": (c_int, [P, P, P, c_int, c_int, c_float, c_long, c_int, P]),
     "ta_trainer_write_snapshot": (c_int, [P, c_int, c_char_p, P, P]),
+    "ta_trainer_write_snapshot_bank": (c_int, [P, c_char_p, P, P, POINTER(c_int)]),
     "ta_trainer_save_checkpoint": (c_int, [P, c_char_p, c_char_p, c_long, c_long, c_int]),
     "ta_trainer_set_meta": (c_int, [P, c_char_p, c_char_p]),
     "ta_base_probe": (c_int, [c_char_p, c_char_p, P, c_char_p, c_int, c_char_p, c_int, c_char_p, c_int]),

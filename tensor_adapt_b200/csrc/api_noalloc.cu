@@ -1,9 +1,8 @@
 // Token-contracted LoRA-gradient GEMM for callers that must not allocate.
 //
-// Who needs this: code that runs where device allocation is forbidden or unsafe - a region that is
-// being captured into a CUDA graph, a latency-critical loop whose owner has handed out all of device
-// memory to its own pool, or a plugin host that pre-sizes memory and treats any cudaMalloc (which
-// also synchronises the whole device) as an error.  The regular entry point ta_gemm_tokens_f32 keeps
+// Who needs this: code that runs where device allocation is forbidden or unsafe - a latency-critical
+// loop whose owner has handed out all of device memory to its own pool, or a plugin host that
+// pre-sizes memory and treats any cudaMalloc (which also synchronises the whole device) as an error.  The regular entry point ta_gemm_tokens_f32 keeps
 // its split-K partials in the context workspace, which is grown with cudaMalloc on demand; this
 // variant keeps them in a fixed array that is part of the library image instead.
 //
@@ -19,6 +18,7 @@ namespace {
 // symbol itself to a kernel.
 static __device__ __align__(256) float g_static_splitk[TA_STATIC_SCRATCH_BYTES / sizeof(float)];
 
+// Written once per device on first use, unsynchronised: contexts are used from one host thread at a time.
 constexpr int kMaxDevices = 64;
 float* g_scratch_ptr[kMaxDevices] = {};
 

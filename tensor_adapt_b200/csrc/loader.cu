@@ -539,7 +539,8 @@ int ta_trainer_counters(ta_trainer* t, long* step, long* tokens_consumed) {
 }
 
 // optimizer.safetensors: "lora.master" / "lora.m" / "lora.v" (F32, the flat arrays with their padding),
-// "centroid.acc" / "centroid.weight" (+ as-built pair), "step" and "tokens_consumed" (I64).
+// "centroid.acc" / "centroid.weight" (+ as-built pair), "step", "tokens_consumed" and "targets" (I64; the
+// TA_TARGET_* mask the flat arrays were laid out for).
 int ta_trainer_save_optimizer(ta_trainer* t, const char* dir) {
     if (!t || !dir) return TA_ERR_INVALID;
     TA_CUDA(t->ctx, cudaStreamSynchronize(t->stream));
@@ -550,7 +551,7 @@ int ta_trainer_save_optimizer(ta_trainer* t, const char* dir) {
         {"lora.master", {"F32", {n}}}, {"lora.m", {"F32", {n}}}, {"lora.v", {"F32", {n}}},
         {"centroid.acc", {"F32", {D}}}, {"centroid.weight", {"F32", {1}}},
         {"centroid_asbuilt.acc", {"F32", {D}}}, {"centroid_asbuilt.weight", {"F32", {1}}},
-        {"step", {"I64", {1}}}, {"tokens_consumed", {"I64", {1}}}};
+        {"step", {"I64", {1}}}, {"tokens_consumed", {"I64", {1}}}, {"targets", {"I64", {1}}}};
     std::vector<size_t> begins;
     const std::string hdr = st_header(tensors, &begins);
     const size_t total = begins.back() + 8;
@@ -559,9 +560,10 @@ int ta_trainer_save_optimizer(ta_trainer* t, const char* dir) {
     const long lens[] = {n, n, n, D, 1, D, 1};
     for (int i = 0; i < 7; i++)
         TA_CUDA(t->ctx, cudaMemcpy(data.data() + begins[size_t(i)], srcs[i], size_t(lens[i]) * 4, cudaMemcpyDeviceToHost));
-    const int64_t step = t->step_count, tok = t->tokens_seen;
+    const int64_t step = t->step_count, tok = t->tokens_seen, tgs = t->ac.targets;
     std::memcpy(data.data() + begins[7], &step, 8);
     std::memcpy(data.data() + begins[8], &tok, 8);
+    std::memcpy(data.data() + begins[9], &tgs, 8);
     const std::string path = std::string(dir) + "/optimizer.safetensors";
     std::ofstream f(path, std::ios::binary);
     if (!f) return fail(t->ctx, TA_ERR_IO, "cannot write " + path);
@@ -591,6 +593,17 @@ int ta_trainer_resume(ta_trainer* t, const char* dir) {
             return fail(t->ctx, TA_ERR_INVALID, "checkpoint alpha does not match the adapter config");
         if (sha && sha->kind == Json::Str && !t->base_sha.empty() && !sha->str.empty() && sha->str != t->base_sha)
             return fail(t->ctx, TA_ERR_INVALID, "checkpoint was trained on another base (base_sha mismatch)");
+        // the set of adapted projections decides the layout of the flat arrays: it must be the same
+        static const struct { const char* key; int bit; } inj[] = {
+            {"inject_q", TA_TARGET_Q}, {"inject_k", TA_TARGET_K}, {"inject_v", TA_TARGET_V}, {"inject_o", TA_TARGET_O},
+            {"inject_gate", TA_TARGET_GATE}, {"inject_up", TA_TARGET_UP}, {"inject_down", TA_TARGET_DOWN}};
+        for (const auto& i : inj) {
+            const Json* v = j.get(i.key);
+            if (!v) continue;
+            if (v->kind != Json::Bool) continue;
+            if (v->b != ((t->ac.targets & i.bit) != 0))
+                return fail(t->ctx, TA_ERR_INVALID, std::string("checkpoint and adapter config disagree on ") + i.key);
+        }
     } else {
         return fail(t->ctx, TA_ERR_IO, "cannot open " + (d / "adapter.json").string());
     }
@@ -613,6 +626,13 @@ int ta_trainer_resume(ta_trainer* t, const char* dir) {
         auto s = wf.entries.find("step"), k = wf.entries.find("tokens_consumed");
         if (s == wf.entries.end() || k == wf.entries.end() || s->second.bytes != 8 || k->second.bytes != 8)
             return fail(t->ctx, TA_ERR_INVALID, "optimizer.safetensors: missing step / tokens_consumed");
+        auto tg = wf.entries.find("targets");
+        if (tg != wf.entries.end() && tg->second.bytes == 8) {
+            int64_t tv;
+            std::memcpy(&tv, tg->second.data, 8);
+            if (int(tv) != t->ac.targets)
+                return fail(t->ctx, TA_ERR_INVALID, "optimizer.safetensors was written for another set of adapted projections");
+        }
         int64_t sv, kv;
         std::memcpy(&sv, s->second.data, 8);
         std::memcpy(&kv, k->second.data, 8);
@@ -654,6 +674,30 @@ int ta_trainer_resume(ta_trainer* t, const char* dir) {
         }
     }
     TA_CUDA(t->ctx, cudaStreamSynchronize(t->stream));   // the mapping goes away on return
+    // Snapshots the interrupted run already wrote (<run>/centroids/step-N.centroid beside <run>/step-N) come back
+    // into the in-memory list in step order, so that the final merge sees the whole run - the reference's
+    // merge_and_write reads the directory when its list is empty (src/centroid/centroid_accumulator.cpp:93-107).
+    t->snapshots.clear();
+    const fs::path cdir = d.parent_path() / "centroids";
+    if (fs::is_directory(cdir, ec)) {
+        std::vector<std::pair<long, fs::path>> files;
+        for (const auto& e : fs::directory_iterator(cdir, ec)) {
+            const std::string name = e.path().filename().string();
+            long sn = -1;
+            if (e.path().extension() == ".centroid" && std::sscanf(name.c_str(), "step-%ld", &sn) == 1 && sn >= 0 && sn <= t->step_count)
+                files.emplace_back(sn, e.path());
+        }
+        std::sort(files.begin(), files.end());
+        for (const auto& f : files) {
+            std::ifstream in(f.second, std::ios::binary);
+            int dd = 0;
+            in.read(reinterpret_cast<char*>(&dd), 4);
+            if (!in || dd != t->mc.hidden) continue;
+            std::vector<float> c(static_cast<size_t>(dd), 0.f);
+            in.read(reinterpret_cast<char*>(c.data()), std::streamsize(size_t(dd) * 4));
+            if (in) t->snapshots.push_back(std::move(c));
+        }
+    }
     return ta_trainer_sync_working(t);
 }
 

@@ -21,6 +21,7 @@ enum DeviceStatus : int {
     DS_TIMEOUT_EPILOGUE = 103,   // epilogue waited too long for an accumulator
     DS_TIMEOUT_SOFTMAX  = 104,   // attention softmax warps waited too long
     DS_BAD_LAUNCH       = 105,   // a kernel was launched with a block size its warp roles do not match
+    DS_TIMEOUT_SELFTEST = 106,   // the self-test kernel's wait on a barrier nobody arrives at (expected)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -71,8 +72,8 @@ constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
 // Bounded wait. `abort_flag` lives in shared memory and is raised by whichever thread of the CTA
 // times out first, so the others stop promptly; `status` is the global status word.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                int* status, int code, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
@@ -81,13 +82,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             if (*abort_flag) return false;
             uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) {
+            else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+    return mbar_wait_limit(bar, parity, abort_flag, status, code, WAIT_LIMIT_NS);
 }
 
 // ── TMA ─────────────────────────────────────────────────────────────────────

@@ -257,6 +257,9 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count) {
             RC(ta_centroid_accumulate(ctx, TA_CENTROID_INTENDED, k.x_normed, t->d_xn, BT, H, t->cen_acc, t->cen_w, s));
         if (t->ac.centroid_modes & 2)
             RC(ta_centroid_accumulate(ctx, TA_CENTROID_ASBUILT, k.x_normed, t->d_xn, BT, H, t->cen_acc_ab, t->cen_w_ab, s));
+        if (t->ac.centroid_modes & 4)   // per-layer bank: the documented sum kept separately for every layer
+            RC(ta_centroid_accumulate(ctx, TA_CENTROID_INTENDED, k.x_normed, t->d_xn, BT, H, t->cen_bank + size_t(l) * H,
+                                      t->cen_bank_w + l, s));
         // grad += rms_norm_bwd(dx_normed, pre_attn_res)                       (:298-304)
         if (l > 0)
             RC(ta_rms_norm_bwd(ctx, t->d_xn, k.r_in, w.input_norm, k.in_rms, t->g_res, t->g_res, BT, H, s));
@@ -359,6 +362,8 @@ int ta_trainer_create(ta_ctx* ctx, const ta_model_config* mc, const ta_adapter_c
         t->working = static_cast<bf16*>(Lo.take(size_t(off) * 2));
         t->cen_acc = static_cast<float*>(Lo.take(size_t(H) * 4));
         t->cen_acc_ab = static_cast<float*>(Lo.take(size_t(H) * 4));
+        t->cen_bank = static_cast<float*>(Lo.take(size_t(Lyr) * H * 4));
+        t->cen_bank_w = static_cast<float*>(Lo.take(size_t(Lyr) * 4));
         t->cen_w = static_cast<float*>(Lo.take(256));
         t->cen_w_ab = t->cen_w + 1;
         t->stats = t->cen_w + 8;
@@ -503,6 +508,8 @@ int ta_trainer_tensor(ta_trainer* t, const char* name, void** dev_ptr, long* row
     else if (n == "centroid.weight") set(t->cen_w, 1, 1, 0);
     else if (n == "centroid_asbuilt.acc") set(t->cen_acc_ab, 1, H, 0);
     else if (n == "centroid_asbuilt.weight") set(t->cen_w_ab, 1, 1, 0);
+    else if (n == "centroid_bank.acc") set(t->cen_bank, c.layers, H, 0);
+    else if (n == "centroid_bank.weight") set(t->cen_bank_w, 1, c.layers, 0);
     else if (n == "cache.dx_attn_in") set(t->d_xn, BT, H, 1);
     else if (n == "cache.loss") set(t->loss, 1, BT, 0);
     else if (n == "cache.dQ") set(t->dQ, BT, qd, 1);

@@ -76,6 +76,7 @@ struct ta_trainer {
     int logit_rows = 0;       // rows of the lm-head chunk buffer
     // centroid accumulator state + step statistics (device) and their pinned host mirror
     float *cen_acc = nullptr, *cen_w = nullptr, *cen_acc_ab = nullptr, *cen_w_ab = nullptr;
+    float *cen_bank = nullptr, *cen_bank_w = nullptr;   // per-layer bank: [layers][hidden] sums and [layers] weights
     float* stats = nullptr;   // [0]=norm [1]=clip scale [2]=loss sum [3]=loss count
     float* h_stats = nullptr;
     // bookkeeping

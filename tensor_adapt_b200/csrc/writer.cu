@@ -216,6 +216,40 @@ int ta_trainer_write_snapshot(ta_trainer* t, int mode, const char* path, float* 
     return TA_OK;
 }
 
+// One record of the reference's snapshot layout per layer, back to back (a "bank"): int32 D | D x f32 | f32 weight.
+// Layers whose weight is still zero are left out, like the reference skips an empty accumulator.
+extern "C" int ta_trainer_write_snapshot_bank(ta_trainer* t, const char* path, float* centroids_out, float* weights_out,
+                                              int* n_records) {
+    if (!t) return TA_ERR_INVALID;
+    if (!(t->ac.centroid_modes & 4)) return fail(t->ctx, TA_ERR_INVALID, "snapshot bank: the trainer was created without centroid mode 4");
+    const int D = t->mc.hidden, L = t->mc.layers;
+    TA_CUDA(t->ctx, cudaStreamSynchronize(t->stream));
+    std::vector<float> acc(size_t(L) * D), w(static_cast<size_t>(L));
+    TA_CUDA(t->ctx, cudaMemcpy(acc.data(), t->cen_bank, acc.size() * 4, cudaMemcpyDeviceToHost));
+    TA_CUDA(t->ctx, cudaMemcpy(w.data(), t->cen_bank_w, w.size() * 4, cudaMemcpyDeviceToHost));
+    for (int l = 0; l < L; l++)
+        if (w[size_t(l)] != 0.f)
+            for (int d = 0; d < D; d++) acc[size_t(l) * D + d] = acc[size_t(l) * D + d] / w[size_t(l)];
+    if (centroids_out) std::memcpy(centroids_out, acc.data(), acc.size() * 4);
+    if (weights_out) std::memcpy(weights_out, w.data(), w.size() * 4);
+    int n = 0;
+    std::ofstream f;
+    if (path) {
+        f.open(path, std::ios::binary);
+        if (!f) return fail(t->ctx, TA_ERR_IO, std::string("cannot write ") + path);
+    }
+    for (int l = 0; l < L; l++) {
+        if (w[size_t(l)] == 0.f) continue;
+        n++;
+        if (!path) continue;
+        f.write(reinterpret_cast<const char*>(&D), 4);
+        f.write(reinterpret_cast<const char*>(acc.data() + size_t(l) * D), std::streamsize(size_t(D) * 4));
+        f.write(reinterpret_cast<const char*>(&w[size_t(l)]), 4);
+    }
+    if (n_records) *n_records = n;
+    return TA_OK;
+}
+
 struct MergeOptions {
     bool extended = false;           // seeded k-means++ / mass ranking instead of the reference's merge
     int init_mode = 0, rank = 0;
@@ -286,6 +320,21 @@ static int merge_dir(ta_ctx* ctx, const char* dir, const char* out_path, int k, 
         f.read(reinterpret_cast<char*>(&w), 4);
         snaps.push_back(std::move(c));
         mass.push_back(w);
+        // A bank file carries further records of the same layout.  The reference's reader stops after the first
+        // (src/centroid/centroid_accumulator.cpp:96-106) and so does the reference-mode merge; the extended merge
+        // clusters every vector of every file.
+        while (mo.extended && f) {
+            int d2 = 0;
+            f.read(reinterpret_cast<char*>(&d2), 4);
+            if (!f || d2 != D) break;
+            std::vector<float> c2(size_t(D), 0.f);
+            f.read(reinterpret_cast<char*>(c2.data()), std::streamsize(size_t(D) * 4));
+            float w2 = 0.f;
+            f.read(reinterpret_cast<char*>(&w2), 4);
+            if (!f) break;
+            snaps.push_back(std::move(c2));
+            mass.push_back(w2);
+        }
     }
     if (n_vectors) *n_vectors = int(snaps.size());
     if (snaps.empty()) return TA_OK;   // the reference logs "no snapshots to merge" and writes nothing

@@ -268,6 +268,15 @@ class AdaptTrainer:
         self._call("ta_trainer_write_snapshot", mode, path, cen.ctypes.data_as(c_void_p), ctypes.byref(w))
         return cen, w.value
 
+    def write_snapshot_bank(self, path: Optional[str] = None):
+        """Per-layer centroid bank (AdapterConfig.centroid_modes bit 2): (centroids [layers, hidden], weights [layers]);
+        `path` receives one reference-layout snapshot record per layer."""
+        L, D = self.model.layers, self.model.hidden
+        cen = np.zeros((L, D), dtype=np.float32); w = np.zeros(L, dtype=np.float32); n = c_int(0)
+        self._call("ta_trainer_write_snapshot_bank", path.encode() if path else None, cen.ctypes.data_as(c_void_p),
+                   w.ctypes.data_as(c_void_p), ctypes.byref(n))
+        return cen, w
+
     def save_checkpoint(self, directory: str, with_optimizer: bool = True) -> None:
         """AdapterWriter::save_checkpoint files, plus optimizer.safetensors (what `resume` needs for an
         exact continuation)."""

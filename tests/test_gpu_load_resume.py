@@ -179,3 +179,43 @@ def test_load_base_vs_reference_golden(ctx, tmp_path):
         bits = o.bf16_bits(tr.download(tname).ravel()).astype("<u2").tobytes()
         assert hashlib.sha256(bits).hexdigest() == want, name
     tr.close()
+
+
+def test_save_adapter_after_resume_merges_the_whole_run(ctx, tmp_path):
+    """A run interrupted after its first snapshot and resumed ends with the same adapter.centroid as the
+    uninterrupted run: the snapshot files already on disk come back into the merge list on resume."""
+    cfg, base, adapter, toks, tgts = _case()
+
+    def run(out, stop_after=None, resume_from=None):
+        tr = _trainer(ctx, cfg); rc.load_into_trainer(tr, cfg, base, adapter if resume_from is None else o.make_adapter(cfg, 16))
+        tr.output_dir, tr.checkpoint_every = str(out), 1
+        first = 0
+        if resume_from is not None:
+            tr.resume(resume_from)
+            first = tr.step_count
+        for s in range(first, 4 if stop_after is None else stop_after):
+            tr.step(toks[s], tgts[s], 2, lr=1e-3)          # writes centroids/step-N.centroid and step-N/ every step
+        if stop_after is None:
+            tr.save_adapter(str(out))
+        tr.close()
+
+    whole, parts = tmp_path / "whole", tmp_path / "parts"
+    run(whole)
+    run(parts, stop_after=2)
+    run(parts, resume_from=str(parts / "step-2"))
+    assert (parts / "adapter.centroid").read_bytes() == (whole / "adapter.centroid").read_bytes()
+    assert o.read_merged_file(str(whole / "adapter.centroid")).shape[0] == 5       # 4 step snapshots + the final one
+
+
+def test_resume_refuses_another_target_set(ctx, tmp_path):
+    from tensor_adapt_b200 import TAError
+    cfg, base, adapter, toks, tgts = _case()
+    a = _trainer(ctx, cfg); rc.load_into_trainer(a, cfg, base, adapter)
+    a.step(toks[0], tgts[0], 2, lr=1e-3)
+    ck = str(tmp_path / "step-1")
+    a.save_checkpoint(ck)
+    a.close()
+    b = _trainer(ctx, cfg, targets=7)                   # q/k/v only: other flat layout
+    with pytest.raises(TAError, match="disagree on inject_o|another set of adapted projections"):
+        b.resume(ck)
+    b.close()

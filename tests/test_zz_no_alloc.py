@@ -1,11 +1,11 @@
 """The allocation-free variant of the token-contracted gradient GEMM (ta_gemm_tokens_f32_static).
 
-Some users of this library run where device allocation is off limits: inside a CUDA-graph capture,
-inside a serving or training process that has already handed every byte of device memory to its own
-pool, or behind a plugin interface that treats cudaMalloc (and the device-wide stall it causes) as a
-fault.  For them the split-K partials live in a fixed array compiled into the library.  This file
+Some users of this library run where device allocation is off limits: inside a serving or training
+process that has already handed every byte of device memory to its own pool, or behind a plugin
+interface that treats cudaMalloc (and the device-wide stall it causes) as a fault.  For them the split-K partials live in a fixed array compiled into the library.  This file
 checks, through the C ABI, that the variant returns what the regular entry point returns - twice in a
-row, because the array keeps the previous call's contents - and that oversized requests are refused
+row, because the array keeps the previous call's contents - that both agree with a plain FP32 product,
+and that oversized requests are refused
 with a readable message instead of overrunning the array.  It is collected last on purpose."""
 import numpy as np
 import pytest
@@ -31,6 +31,8 @@ def test_static_scratch_variant_matches_regular_entry_point(ctx):
         C0 = torch.randn(shape, device="cuda")
         ref = C0.clone()
         ctx.call("ta_gemm_tokens_f32", M, N, K, 2.0, ptr(A), M, ptr(B), N, ptr(ref), shape[1], 1, int(transpose), stream_ptr())
+        prod = 2.0 * (A.float().t() @ B.float())                     # [M, N] in plain FP32 arithmetic
+        exact = C0 + (prod.t() if transpose else prod)
         for attempt in range(2):
             out = C0.clone()
             ctx.call("ta_gemm_tokens_f32_static", M, N, K, 2.0, ptr(A), M, ptr(B), N, ptr(out), shape[1], 1, int(transpose),
@@ -40,6 +42,8 @@ def test_static_scratch_variant_matches_regular_entry_point(ctx):
             # regular entry point is tested with
             err = (out - ref).abs().max().item()
             assert err <= 1e-4 * ref.abs().max().item() + 1e-4, (M, N, K, transpose, attempt, err)
+            # and on its own feet: against the FP32 product (only the summation order differs)
+            assert (out - exact).abs().max().item() <= 1e-3 * exact.abs().max().item(), (M, N, K, transpose, attempt)
     ctx.check_device()
 
 
