@@ -213,6 +213,11 @@ def main():
     ap.add_argument("--config", default="qwen2-7b", choices=sorted(CONFIGS))
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="library", choices=["library", "torch"],
+                    help="gradient exchange for N > 1: the library's per-layer NCCL buckets overlapped with the backward, "
+                         "or one torch.distributed all-reduce after it")
+    ap.add_argument("--cadence", type=int, default=0,
+                    help="write a centroid snapshot and (rank 0) a checkpoint every this many steps inside the timed region")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -221,7 +226,7 @@ def main():
     import torch
     import torch.distributed as dist
     import tensor_adapt_b200 as ta
-    from tensor_adapt_b200.dp import shard_batch
+    from tensor_adapt_b200.dp import Comm, shard_batch
     from tensor_adapt_b200.trainer import QWEN2, AdaptTrainer, AdapterConfig
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -251,7 +256,7 @@ def main():
     ctx = ta.Context(local)
     stream = torch.cuda.current_stream().cuda_stream
     ac = AdapterConfig.defaults(rank=lrank, alpha=alpha, targets=targets, lr=2e-4, weight_decay=0.01, centroid_modes=1)
-    tr = AdaptTrainer(ctx, mc, ac, micro, T, stream=stream)
+    tr = AdaptTrainer(ctx, mc, ac, micro, T, stream=stream, output_dir=tempfile.mkdtemp() if args.cadence else None)
     tr.init_random(seed=1, std=0.02)
     # B != 0 so that every LoRA product does real work from the first step
     g = torch.Generator(device="cuda").manual_seed(7)
@@ -259,6 +264,10 @@ def main():
     tr.sync_working()
     grad = tr.torch_view("lora.grad")
     loss_stats = tr.torch_view("step.stats")[2:4]      # (sum of per-token losses, their count) of this rank's shard
+    comm = None
+    if world > 1 and args.exchange == "library":
+        comm = Comm(ctx, rank, world)
+        tr._call("ta_trainer_set_comm", comm.h)        # forward_backward now reduces each layer's slice as it completes
 
     gen = np.random.default_rng(1234)
     host_batches, dev_batches = [], []
@@ -273,10 +282,27 @@ def main():
         tok, tgt = (host_batches if host else dev_batches)[i & 1]
         tr.zero_grad()
         tr.forward_backward(tok, tgt, b_local, global_tokens=global_tokens)
-        if world > 1:
+        if world > 1 and comm is None:
             dist.all_reduce(grad)
             dist.all_reduce(loss_stats)                # so the reported loss is the global-batch mean on every rank
-        return tr.optimizer_step(2e-4)
+        m = tr.optimizer_step(2e-4)
+        if args.cadence and m.step % args.cadence == 0:
+            cadence_event(m.step)
+        return m
+
+    cadence_ms = []
+
+    def cadence_event(step):
+        """What AdaptTrainer does every checkpoint_every steps (src/trainer/adapt_trainer.cu:265-270): a centroid
+        snapshot (sums reduced over the ranks first) and, on rank 0, the checkpoint files."""
+        t0 = time.perf_counter()
+        if world > 1:
+            for name in ("centroid.acc", "centroid.weight"):
+                dist.all_reduce(tr.torch_view(name).clone())
+        tr.write_snapshot(step)
+        if rank == 0:
+            tr.save_checkpoint(os.path.join(tr.output_dir, f"step-{step}"))
+        cadence_ms.append((time.perf_counter() - t0) * 1e3)
 
     def timed(n, host):
         if world > 1:
@@ -330,6 +356,12 @@ def main():
                                    f"{bin(targets).count('1')} projections, global batch {gbatch} x {T} tokens, "
                                    f"micro-batch {micro} sequences, AdamW + grad clip + centroid accumulator",
                        "global_batch": gbatch, "seq_len": T, "micro_batch": micro, "parallelism": f"dp{world}",
+                       "exchange": ("none" if world == 1 else "library: per-layer NCCL all-reduce buckets on a second stream, "
+                                    "overlapped with the backward" if comm is not None else "torch.distributed all-reduce after the backward"),
+                       "cadence": ({"every_steps": args.cadence, "events_in_timed_regions": len(cadence_ms),
+                                    "ms_per_event": (sum(cadence_ms) / len(cadence_ms)) if cadence_ms else None,
+                                    "what": "centroid snapshot + rank-0 checkpoint (adapter.safetensors, adapter.json, "
+                                            "train_state.json, optimizer.safetensors)"} if args.cadence else None),
                        "l2": "per-step working set (>=15 GB of weights + activations) far exceeds the 126 MB L2; no flush needed",
                        "loss": m.loss, "grad_norm": m.grad_norm_raw},
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e,
@@ -359,6 +391,8 @@ def main():
                 line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
         print(json.dumps(line))
     tr.close()
+    if comm is not None:
+        comm.close()
     ctx.close()
     if world > 1:
         dist.destroy_process_group()

@@ -334,6 +334,30 @@ int ta_trainer_set_meta(ta_trainer* tr, const char* arch_name, const char* base_
  * (centroid_accumulator.cpp:93-168 as called from AdaptTrainer::save_adapter, adapt_trainer.cu:322-325). */
 int ta_trainer_merge_snapshots(ta_trainer* tr, int k, const char* out_path, int* passes);
 
+/* ── data-parallel exchange ────────────────────────────────────────────────────────────────
+ * The reference has no multi-GPU code; nothing here replaces a reference interface.  One process per GPU; every
+ * rank holds the frozen base and the LoRA state, takes its shard of the global batch, scales its cross-entropy
+ * gradient by 1/global_tokens (ta_trainer_forward_backward) and the flat FP32 gradient array is SUM-reduced with
+ * NCCL, together with the (loss sum, loss count) pair, before the replicated optimiser step.  NCCL is loaded at
+ * run time (the copy already in the process, else libnccl.so.2); without it these calls return
+ * TA_ERR_UNSUPPORTED and everything else works. */
+typedef struct ta_comm ta_comm;
+/* ncclGetUniqueId: rank 0 fills `out` (>= 128 bytes) and hands the bytes to the other ranks by any host channel. */
+int ta_comm_unique_id(void* out, size_t bytes);
+/* ncclCommInitRank on the context's device, plus the side stream the exchange runs on. Collective: every rank calls it. */
+int ta_comm_create(ta_ctx* ctx, int rank, int world, const void* unique_id, size_t bytes, ta_comm** out);
+int ta_comm_destroy(ta_comm* comm);
+int ta_comm_info(const ta_comm* comm, int* rank, int* world);
+/* One in-place all-reduce of "lora.grad" and of step.stats[2:4], ordered after the trainer's stream and awaited by
+ * it: call between ta_trainer_forward_backward and ta_trainer_optimizer_step. */
+int ta_allreduce_grads(ta_trainer* tr, ta_comm* comm);
+/* Attach (or with NULL detach) a communicator: ta_trainer_forward_backward then performs the exchange itself,
+ * bucketed per layer - the slice of a layer is all-reduced on the communicator's stream as soon as that layer's
+ * backward has been issued in the LAST micro-batch of the call, overlapping the transfer with the remaining
+ * layers - and the trainer's stream waits for the last bucket.  Requires ONE forward_backward call per optimiser
+ * step (the call's micro-batches accumulate; a second call would add to already-reduced gradients). */
+int ta_trainer_set_comm(ta_trainer* tr, ta_comm* comm);
+
 /* ── real weights and resume ─────────────────────────────────────────────────────────────── */
 /* parser::ModelConfig::from_dir + the derived fields of base::BaseLoader::load
  * (src/parser/config.cpp:43-110,132-134; src/base/base_loader.cpp:90-110,160): reads <dir>/config.json with

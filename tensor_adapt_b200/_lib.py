@@ -74,6 +74,12 @@ _PROTOS = {
                                        c_float, P, c_int, P]),
     "ta_centroid_accumulate": (c_int, [P, c_int, P, P, c_int, c_int, P, P, P]),
     "ta_kmeans_merge": (c_int, [P, P, c_int, c_int, c_int, c_int, P, P, POINTER(c_int), POINTER(c_int), P]),
+    "ta_comm_unique_id": (c_int, [P, c_size_t]),
+    "ta_comm_create": (c_int, [P, c_int, c_int, P, c_size_t, POINTER(c_void_p)]),
+    "ta_comm_destroy": (c_int, [P]),
+    "ta_comm_info": (c_int, [P, POINTER(c_int), POINTER(c_int)]),
+    "ta_allreduce_grads": (c_int, [P, P]),
+    "ta_trainer_set_comm": (c_int, [P, P]),
     "ta_trainer_create": (c_int, [P, P, P, c_int, c_int, P, POINTER(c_void_p)]),
     "ta_trainer_destroy": (c_int, [P]),
     "ta_trainer_init_random": (c_int, [P, ctypes.c_ulonglong, c_float]),

@@ -187,7 +187,9 @@ int proj_bwd_group(ta_trainer* t, int l, const bf16* x, const BwdProj* ps, int n
 }
 
 // forward + loss + backward for one micro-batch already resident in t->tok / t->tgt
-int run_micro(ta_trainer* t, int Bm, int T, float inv_count) {
+// `exchange`: this is the last micro-batch of the optimiser step and a communicator is attached - each layer's
+// gradient slice is all-reduced on the communicator's stream as soon as that layer's backward has been issued.
+int run_micro(ta_trainer* t, int Bm, int T, float inv_count, bool exchange) {
     const ta_model_config& c = t->mc;
     ta_ctx* ctx = t->ctx;
     void* s = t->stream;
@@ -263,7 +265,9 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count) {
         // grad += rms_norm_bwd(dx_normed, pre_attn_res)                       (:298-304)
         if (l > 0)
             RC(ta_rms_norm_bwd(ctx, t->d_xn, k.r_in, w.input_norm, k.in_rms, t->g_res, t->g_res, BT, H, s));
+        if (exchange) RC(comm_reduce_slice(t, t->layer_begin[size_t(l)], t->layer_begin[size_t(l) + 1]));
     }
+    if (exchange) RC(comm_finish_step(t));
     (void)qd; (void)kv;
     return TA_OK;
 }
@@ -334,8 +338,10 @@ int ta_trainer_create(ta_ctx* ctx, const ta_model_config* mc, const ta_adapter_c
         t->fuse_gu = on(T_GATE) && on(T_UP);
         long off = 0;
         size_t sk_need = 0;
+        t->layer_begin.assign(size_t(Lyr) + 1, 0);
         static const int kGroups[4][3] = {{T_Q, T_K, T_V}, {T_O, -1, -1}, {T_GATE, T_UP, -1}, {T_DOWN, -1, -1}};
-        for (int l = 0; l < Lyr; l++)
+        for (int l = 0; l < Lyr; l++) {
+            t->layer_begin[size_t(l)] = off;
             for (const auto& grp : kGroups) {
                 int members[3], nm = 0;
                 for (int tg : grp) if (tg >= 0 && on(tg)) members[nm++] = tg;
@@ -354,6 +360,8 @@ int ta_trainer_create(ta_ctx* ctx, const ta_model_config* mc, const ta_adapter_c
                                         tokens_gemm_ws_bytes_max(ctx, sl.in, fused ? nm * r : r)});
                 }
             }
+        }
+        t->layer_begin[size_t(Lyr)] = off;
         t->lora_n = off;
         t->master = static_cast<float*>(Lo.take(size_t(off) * 4));
         t->m = static_cast<float*>(Lo.take(size_t(off) * 4));
@@ -595,7 +603,7 @@ int ta_trainer_forward_backward(ta_trainer* t, const int* tokens, const int* tar
         const size_t bytes = size_t(Bm) * T * sizeof(int);
         TA_CUDA(t->ctx, cudaMemcpyAsync(t->tok, tokens + size_t(b0) * T, bytes, kind, t->stream));
         TA_CUDA(t->ctx, cudaMemcpyAsync(t->tgt, targets + size_t(b0) * T, bytes, kind, t->stream));
-        if (int rc = run_micro(t, Bm, T, inv)) return rc;
+        if (int rc = run_micro(t, Bm, T, inv, t->comm != nullptr && b0 + t->micro_B >= B)) return rc;
     }
     return TA_OK;
 }

@@ -43,6 +43,14 @@ struct DeviceArena {
 
 }  // namespace ta
 
+struct ta_comm;
+
+namespace ta {
+// csrc/comm.cu: bucketed gradient exchange on the attached communicator (no-ops without one)
+int comm_reduce_slice(ta_trainer* t, long lo, long hi);
+int comm_finish_step(ta_trainer* t);
+}  // namespace ta
+
 struct ta_trainer {
     ta_ctx* ctx = nullptr;
     cudaStream_t stream = nullptr;
@@ -79,6 +87,9 @@ struct ta_trainer {
     float *cen_bank = nullptr, *cen_bank_w = nullptr;   // per-layer bank: [layers][hidden] sums and [layers] weights
     float* stats = nullptr;   // [0]=norm [1]=clip scale [2]=loss sum [3]=loss count
     float* h_stats = nullptr;
+    // data parallelism: communicator attached with ta_trainer_set_comm, first element of every layer's gradient slice
+    ta_comm* comm = nullptr;
+    std::vector<long> layer_begin;   // [layers + 1] element offsets into the flat LoRA arrays
     // bookkeeping
     long step_count = 0, tokens_seen = 0;
     long pending_tokens = 0;  // tokens of the optimiser step in progress, added to tokens_seen when it completes

@@ -32,6 +32,37 @@ def allreduce_sum_(tensors, group=None):
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
 
 
+class Comm:
+    """NCCL communicator owned by the C library (ta_comm_*): rank 0 draws the unique id, the bytes travel to the
+    other ranks over the already-initialised torch.distributed group (any backend; gloo is enough)."""
+
+    def __init__(self, ctx, rank: int, world: int, group=None):
+        import ctypes
+        import torch
+        import torch.distributed as dist
+        from ._lib import lib, TAError
+        buf = (ctypes.c_ubyte * 128)()
+        if rank == 0:
+            rc = lib.ta_comm_unique_id(buf, 128)
+            if rc:
+                raise TAError(rc, "ta_comm_unique_id (is NCCL loadable?)")
+        if world > 1:
+            t = torch.tensor(list(buf), dtype=torch.uint8)
+            if dist.get_backend(group) == "nccl":
+                t = t.cuda()
+            dist.broadcast(t, src=0, group=group)
+            buf = (ctypes.c_ubyte * 128)(*t.cpu().tolist())
+        h = ctypes.c_void_p()
+        ctx.call("ta_comm_create", rank, world, buf, 128, ctypes.byref(h))
+        self.h, self.ctx, self.rank, self.world = h, ctx, rank, world
+
+    def close(self):
+        if self.h:
+            from ._lib import lib
+            lib.ta_comm_destroy(self.h)
+            self.h = None
+
+
 class DataParallelStep:
     """zero_grad -> local forward/backward on this rank's shard -> all-reduce -> optimiser step.
 
@@ -39,17 +70,22 @@ class DataParallelStep:
     reports the global-batch mean loss of src/trainer/adapt_trainer.cu:237-246.  Reduced per snapshot:
     the centroid sums (`write_snapshot`); each rank keeps its own running sums in between."""
 
-    def __init__(self, trainer, rank: int, world: int, group=None):
-        self.tr, self.rank, self.world, self.group = trainer, rank, world, group
+    def __init__(self, trainer, rank: int, world: int, group=None, comm: "Comm | None" = None):
+        """With `comm` the exchange runs inside the library: per-layer buckets all-reduced on a second stream while
+        the backward of the remaining layers proceeds (ta_trainer_set_comm); without it, one torch all-reduce."""
+        self.tr, self.rank, self.world, self.group, self.comm = trainer, rank, world, group, comm
         self.grad = trainer.torch_view("lora.grad")
         self.stats = trainer.torch_view("step.stats")
+        if comm is not None:
+            trainer._call("ta_trainer_set_comm", comm.h)
 
     def step(self, tokens, targets, global_batch: int, lr: float = -1.0, total_steps: int = 0):
         tr = self.tr
         tok, tgt, b_local = shard_batch(tokens, targets, global_batch, tr.seq_len, self.rank, self.world)
         tr.zero_grad()
         tr.forward_backward(tok, tgt, b_local, global_tokens=global_batch * tr.seq_len)
-        allreduce_sum_([self.grad, self.stats[2:4]], self.group)
+        if self.comm is None:
+            allreduce_sum_([self.grad, self.stats[2:4]], self.group)
         return tr.optimizer_step(lr, total_steps)
 
     def write_snapshot(self, step: int, mode: int = 0):

@@ -11,11 +11,11 @@ for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")):
     sys.path.insert(0, p)
 import refcase as rc  # noqa: E402
 import tensor_adapt_b200 as ta  # noqa: E402
-from tensor_adapt_b200.dp import DataParallelStep  # noqa: E402
+from tensor_adapt_b200.dp import Comm, DataParallelStep  # noqa: E402
 from tensor_adapt_b200.trainer import AdaptTrainer, AdapterConfig  # noqa: E402
 
 
-def main(out_path):
+def main(out_path, exchange="torch"):
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -26,7 +26,8 @@ def main(out_path):
     ac = AdapterConfig.defaults(rank=rank_r, alpha=32.0, targets=15, lr=2e-4, weight_decay=0.01, centroid_modes=1)
     tr = AdaptTrainer(ctx, rc.model_config(cfg), ac, B // world, T, stream=torch.cuda.current_stream().cuda_stream)
     rc.load_into_trainer(tr, cfg, base, adapter)
-    dp = DataParallelStep(tr, rank, world)
+    comm = Comm(ctx, rank, world) if exchange == "library" else None      # C-level NCCL, per-layer overlapped buckets
+    dp = DataParallelStep(tr, rank, world, comm=comm)
     out = {}
     for s in range(2):
         m = dp.step(toks[s], tgts[s], B, lr=2e-4)
@@ -42,9 +43,12 @@ def main(out_path):
     if rank == 0:
         np.savez(out_path, **out)
     dist.barrier()
-    tr.close(); ctx.close()
+    tr.close()
+    if comm is not None:
+        comm.close()
+    ctx.close()
     dist.destroy_process_group()
 
 
 if __name__ == "__main__":
-    main(sys.argv[1])
+    main(*sys.argv[1:3])
