@@ -226,7 +226,7 @@ def main():
     import torch
     import torch.distributed as dist
     import tensor_adapt_b200 as ta
-    from tensor_adapt_b200.dp import Comm, shard_batch
+    from tensor_adapt_b200.dp import Comm, DataParallelStep, shard_batch
     from tensor_adapt_b200.trainer import QWEN2, AdaptTrainer, AdapterConfig
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -291,15 +291,13 @@ def main():
         return m
 
     cadence_ms = []
+    snapshotter = DataParallelStep(tr, rank, world, comm=comm)
 
     def cadence_event(step):
         """What AdaptTrainer does every checkpoint_every steps (src/trainer/adapt_trainer.cu:265-270): a centroid
         snapshot (sums reduced over the ranks first) and, on rank 0, the checkpoint files."""
         t0 = time.perf_counter()
-        if world > 1:
-            for name in ("centroid.acc", "centroid.weight"):
-                dist.all_reduce(tr.torch_view(name).clone())
-        tr.write_snapshot(step)
+        snapshotter.write_snapshot(step)               # sums of all ranks; rank 0 writes the file
         if rank == 0:
             tr.save_checkpoint(os.path.join(tr.output_dir, f"step-{step}"))
         cadence_ms.append((time.perf_counter() - t0) * 1e3)
