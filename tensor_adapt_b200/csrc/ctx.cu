@@ -163,7 +163,7 @@ int ta_ctx_set_gemm_tuning(ta_ctx* ctx, int tile_n, int tile_m_halves, int cta_p
     if (!none && !ok) return ta::fail(ctx, TA_ERR_INVALID, "gemm tuning: tile_n in {64,128,224,256}, halves 1 or 2 (2 needs tile_n >= 224)");
     ctx->gemm_force_bn = tile_n;
     ctx->gemm_force_mh = tile_m_halves;
-    ctx->gemm_pair = cta_pair != 0;
+    ctx->gemm_pair = cta_pair;
     return TA_OK;
 }
 

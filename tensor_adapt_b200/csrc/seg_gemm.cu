@@ -495,6 +495,176 @@ done:
     }
 }
 
+// ── CTA-pair kernel, 256 x BN pair tile, double-buffered accumulators ───────
+// The same pairing (cluster of two, tcgen05.mma.cta_group::2 with M = 256, half of every B tile per CTA, no
+// multicast load), but each CTA owns only 128 rows, so one accumulator takes BN <= 256 of its 512 tensor-memory
+// columns and a second one is free: the epilogue of tile i (TMEM -> registers -> global) overlaps the main loop of
+// tile i+1, which the 256-row single-CTA tiles (all 512 columns in use) cannot do.  Per FLOP a CTA fills the same
+// shared memory as the 256-row kernel and the tensor core reads a third less of it.  One MMA per 16 k (the
+// single-CTA 256-row kernel issues two).  K-major A only; B K-major or MN-major; no split-K.
+//
+// Barriers as in the kernel above: full[s] in rank 0 (count 2: one arrive.expect_tx per CTA, both CTAs' loads
+// complete on it); empty[s] and tfull[b] in each CTA (rank 0 commits to both); tempty[b] in rank 0 (the epilogue
+// warps of both CTAs arrive there).
+template <int BN>
+struct Pair2Cfg {
+    static constexpr int STAGES = 6;
+    static constexpr uint32_t A_BYTES = 128 * BK * 2;
+    static constexpr uint32_t B_BYTES = 128 * BK * 2;              // half tile: BN/2 <= 128 rows, or two 64-column chunks
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    seg_gemm_pair2_kernel(const __grid_constant__ SegGemmParams p) {
+    using C = Pair2Cfg<BN>;
+    constexpr int HALF = BN / 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* tfull = empty + C::STAGES;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(&full[s], 2);      // one arrive.expect_tx from each CTA's producer
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], 16);   // eight epilogue warps in each CTA
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                  // the peer's barriers are initialised before anything arrives on them
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int m_tiles = (p.M + 255) / 256;
+    const int n_tiles = (p.N + BN - 1) / BN;
+    const int total = m_tiles * n_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int s = 0; s < p.nseg; s++) {
+                prefetch_tensormap(&p.tmA[s]);
+                prefetch_tensormap(&p.tmB[s]);
+            }
+            uint32_t it = 0;
+            for (int tile = pair; tile < total; tile += npairs) {
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, BN);
+                const int m0 = tc.m0 + int(rank) * 128, nh = tc.n0 + int(rank) * HALF;
+                for (int s = 0; s < p.nseg; s++) {
+                    const int nkb = (p.K[s] + BK - 1) / BK;
+                    const bool b_mn = p.b_mn[s] != 0;
+                    for (int kb = 0; kb < nkb; kb++, it++) {
+                        const uint32_t stage = it % C::STAGES;
+                        const uint32_t ph = (it / C::STAGES) & 1u;
+                        if (!mbar_wait(&empty[stage], ph ^ 1u, abort_flag, p.status, DS_TIMEOUT_PRODUCER)) goto done;
+                        uint8_t* sa = smem + stage * C::STAGE_BYTES;
+                        uint8_t* sb = sa + C::A_BYTES;
+                        const uint32_t fbar = map_to_cta(smem_u32(&full[stage]), 0);
+                        mbar_arrive_expect_tx_cluster(fbar, C::STAGE_BYTES);
+                        tma_load_2d_pair(sa, &p.tmA[s], fbar, kb * BK, m0);             // box {64, 128}
+                        if (!b_mn) {
+                            tma_load_2d_pair(sb, &p.tmB[s], fbar, kb * BK, nh);         // box {64, 128}
+                        } else {
+                            tma_load_2d_pair(sb, &p.tmB[s], fbar, nh, kb * BK);         // box {64, 64} x 2
+                            tma_load_2d_pair(sb + 8192, &p.tmB[s], fbar, nh + 64, kb * BK);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t peer_empty0 = map_to_cta(smem_u32(&empty[0]), 1), peer_tfull0 = map_to_cta(smem_u32(&tfull[0]), 1);
+            uint32_t it = 0, lt = 0;
+            for (int tile = pair; tile < total; tile += npairs, lt++) {
+                const uint32_t buf = lt & 1u, use = lt >> 1;
+                if (!mbar_wait(&tempty[buf], (use & 1u) ^ 1u, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
+                tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                uint32_t acc = 0;
+                for (int s = 0; s < p.nseg; s++) {
+                    const int nkb = (p.K[s] + BK - 1) / BK;
+                    const bool b_mn = p.b_mn[s] != 0;
+                    const uint32_t idesc = umma_idesc_bf16(256, BN, false, b_mn);
+                    for (int kb = 0; kb < nkb; kb++, it++) {
+                        const uint32_t stage = it % C::STAGES;
+                        const uint32_t ph = (it / C::STAGES) & 1u;
+                        if (!mbar_wait(&full[stage], ph, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
+                        tcgen05_fence_after_sync();
+                        const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                        const uint32_t sb = sa + C::A_BYTES;
+                        const int krem = p.K[s] - kb * BK;
+                        const int kinstr = krem >= BK ? 4 : (krem + 15) / 16;
+                        for (int ki = 0; ki < kinstr; ki++) {
+                            const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
+                                                     : smem_desc_sw128(sb + ki * 32, 16, 1024);
+                            umma_bf16_pair(d_tmem, smem_desc_sw128(sa + ki * 32, 16, 1024), bd, idesc, acc);
+                            acc = 1;
+                        }
+                        umma_commit_pair(smem_u32(&empty[stage]));
+                        umma_commit_pair(peer_empty0 + stage * 8);
+                    }
+                }
+                umma_commit_pair(smem_u32(&tfull[buf]));
+                umma_commit_pair(peer_tfull0 + buf * 8);
+            }
+        }
+    } else {
+        // eight epilogue warps per CTA: two per TMEM lane group, each draining half of the columns
+        const int lg = warp & 3;
+        const int eh = (warp - 2) >> 2;
+        const uint32_t tempty0 = map_to_cta(smem_u32(&tempty[0]), 0);
+        constexpr int NCH = BN / 32;
+        const int c_lo = eh * ((NCH + 1) / 2), c_hi = eh == 0 ? (NCH + 1) / 2 : NCH;
+        uint32_t lt = 0;
+        for (int tile = pair; tile < total; tile += npairs, lt++) {
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, BN);
+            const uint32_t buf = lt & 1u, use = lt >> 1;
+            if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
+            tcgen05_fence_after_sync();
+            const int row = tc.m0 + int(rank) * 128 + lg * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * 256u + (uint32_t(lg * 32) << 16);
+            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, c_lo, c_hi);
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + buf * 8);
+        }
+    }
+
+done:
+    __syncwarp();
+    if (*abort_flag) {
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                  // neither CTA leaves while the other may still signal or read it
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
 // Fixed-order reduction of split-K partials: out (+)= sum_s ws[s][m][n]; optional transposed store.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, long split_stride, int M, int N,
                                      float* __restrict__ out, long ldo, int transpose, int accumulate) {
@@ -537,6 +707,21 @@ int launch_pair(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int to
     const int grid = 2 * std::min(total_pair_tiles, ctx->sm_count / 2);
     seg_gemm_pair_kernel<BN><<<grid, kGemmThreads, PairCfg<BN>::SMEM, stream>>>(p);
     TA_LAUNCH_CHECK(ctx, "seg_gemm_pair_kernel");
+    return TA_OK;
+}
+
+template <int BN>
+int launch_pair2(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int total_pair_tiles) {
+    static bool attr_set[64] = {};   // per-device, written on first use from the context's one host thread
+    const int dev = ctx->device & 63;
+    if (!attr_set[dev]) {
+        TA_CUDA(ctx, cudaFuncSetAttribute(seg_gemm_pair2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          int(Pair2Cfg<BN>::SMEM)));
+        attr_set[dev] = true;
+    }
+    const int grid = 2 * std::min(total_pair_tiles, ctx->sm_count / 2);
+    seg_gemm_pair2_kernel<BN><<<grid, kGemmThreads, Pair2Cfg<BN>::SMEM, stream>>>(p);
+    TA_LAUNCH_CHECK(ctx, "seg_gemm_pair2_kernel");
     return TA_OK;
 }
 
@@ -627,7 +812,8 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     const int bn = tcfg.bn, tile_m = 128 * tcfg.mh;
     // CTA-pair kernel (512 x 256 tiles over two SMs): same A boxes as the 256-row kernel, half-width B boxes.
     // Opt-in (ta_ctx_set_gemm_tuning): measured 3-7 % slower than the single-CTA 256-row kernel on the 7B shapes.
-    const bool use_pair = ctx->gemm_pair && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
+    const bool use_pair2 = ctx->gemm_pair == 2 && bn == 256 && tcfg.mh == 2 && out.split_k <= 1 && M >= 256 && (ctx->sm_count % 2) == 0;
+    const bool use_pair = ctx->gemm_pair == 1 && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
     SegGemmParams p;
     std::memset(&p, 0, sizeof(p));
     for (int s = 0; s < nseg; s++) {
@@ -639,10 +825,10 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
             return fail(ctx, TA_ERR_INVALID, "seg_gemm: MN-major A needs M % 8 == 0");
         int rc;
         auto get_tmap_bf16 = out.no_host_state ? encode_tmap_bf16 : ta::get_tmap_bf16;
-        if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, uint32_t(tile_m), &p.tmA[s]);
+        if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, uint32_t(use_pair2 ? 128 : tile_m), &p.tmA[s]);
         else         rc = get_tmap_bf16(ctx, g.A, uint64_t(M), uint64_t(g.K), uint64_t(g.lda) * 2, 64, 64, &p.tmA[s]);
         if (rc) return rc;
-        if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(use_pair ? bn / 2 : bn), &p.tmB[s]);
+        if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(use_pair || use_pair2 ? bn / 2 : bn), &p.tmB[s]);
         else         rc = get_tmap_bf16(ctx, g.B, uint64_t(N), uint64_t(g.K), uint64_t(g.ldb) * 2, 64, 64, &p.tmB[s]);
         if (rc) return rc;
         p.K[s] = g.K;
@@ -676,7 +862,9 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     for (int s = 0; s < nseg; s++) ksum += segs[s].K;
     ProfScope prof(out.no_host_state ? nullptr : ctx, stream, bn >= 128 ? PROF_GEMM : PROF_GEMM_SKINNY, 2.0 * M * N * ksum);
     int rc;
-    if (use_pair) {
+    if (use_pair2) {
+        rc = launch_pair2<256>(ctx, stream, p, ((M + 255) / 256) * n_tiles);
+    } else if (use_pair) {
         rc = launch_pair<256>(ctx, stream, p, ((M + 511) / 512) * n_tiles);
     } else if (tcfg.mh == 2) {
         rc = bn == 224 ? launch<224, 2>(ctx, stream, p, total) : launch<256, 2>(ctx, stream, p, total);

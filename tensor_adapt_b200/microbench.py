@@ -73,7 +73,12 @@ def gemm(ctx, a):
     C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     f = lambda: ctx.call("ta_gemm_bf16", M, N, K, 1.0, ptr(A), K, 0, ptr(Bm), Bm.shape[1], a.b_layout, None, None, ptr(C), N,
                          stream_ptr())
-    report("gemm_bf16", timeit(f, a.iters, a.warmup, a.flush), flops=2.0 * M * N * K, shape=[M, N, K], b_layout=a.b_layout)
+    if a.tile:
+        bn, mh = (int(v) for v in a.tile.split(","))
+        ctx.call("ta_ctx_set_gemm_tuning", bn, mh, a.pair)
+    report("gemm_bf16", timeit(f, a.iters, a.warmup, a.flush), flops=2.0 * M * N * K, shape=[M, N, K], b_layout=a.b_layout,
+           tile=a.tile or "auto", pair=a.pair)
+    ctx.call("ta_ctx_set_gemm_tuning", 0, 0, 0)
 
 
 def lora(ctx, a):
@@ -171,6 +176,8 @@ def main():
             for k, v in (("M", 16384), ("N", 3584), ("K", 3584)):
                 s.add_argument("--" + k, type=int, default=v)
             s.add_argument("--b-layout", type=int, default=0)
+            s.add_argument("--tile", default="", help='force a tile "BN,MH" (experiment knob)')
+            s.add_argument("--pair", type=int, default=0, help="CTA-pair kernel: 0 off, 1 = 512x256 pair tiles, 2 = 256x256")
         elif name == "kmeans":
             for k, v in (("N", 2048), ("D", 512), ("k", 8)):
                 s.add_argument("--" + k, type=int, default=v)
