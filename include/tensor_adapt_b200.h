@@ -169,6 +169,21 @@ int ta_lora_linear_bwd(ta_ctx* ctx, const void* x, const void* dY, const void* W
                        int accumulate_dx, float* gA, float* gB, int BT, int in_dim, int out_dim, int rank, float scale,
                        void* stream);
 
+/* proj_fwd x 2 + apply_lora_fwd x 2 + ops::silu_mul_fwd of the MLP (src/base/arch/qwen2.cu:137-147,
+ * src/backend/cuda/ops.cu:913-923) as one launch: every tile holds 128 gate columns and the 128 matching up columns,
+ * and the epilogue stores gate, up (both needed by the backward) and act = silu(gate) * up.
+ *     gate = x.gate_w^T + scale*(x.A_gate^T).B_gate^T      up likewise      act[BT, inter]
+ * A_gate_up is the two adapters' A blocks back to back, [2*rank][in_dim] (NULL: no adapters); rank % 16 == 0; BT >= 256. */
+int ta_swiglu_proj_fwd(ta_ctx* ctx, const void* x, const void* gate_w, const void* up_w, const void* A_gate_up, const void* B_gate,
+                       const void* B_up, void* gate, void* up, void* act, int BT, int in_dim, int inter, int rank, float scale,
+                       void* stream);
+/* proj_bwd_x of the down projection (+ the dX share of apply_lora_bwd) + ops::silu_mul_bwd (qwen2.cu:221-230,
+ * ops.cu:925-941) as one launch: d_act = dY.down_w (+ dh.A_down) stays in tensor memory and the epilogue writes
+ *     d_gate = d_act * up * silu'(gate)      d_up = d_act * silu(gate)
+ * dY [BT, hidden], down_w [hidden, inter], dh [BT, rank] = bf16(scale*dY.B_down) or NULL, A_down [rank, inter]. */
+int ta_swiglu_down_bwd(ta_ctx* ctx, const void* dY, const void* down_w, const void* dh, const void* A_down, const void* gate,
+                       const void* up, void* d_gate, void* d_up, int BT, int hidden, int inter, int rank, void* stream);
+
 /* ── attention ─────────────────────────────────────────────────────────────────────────────
  * ops::sdpa_fwd / ops::sdpa_bwd (ops.hpp:52-70, src/backend/cuda/ops.cu:578-907): causal GQA
  * attention, scale 1/sqrt(head_dim), Q/out [B*T, Hq*hd], K/V [B*T, Hkv*hd]. Instead of the
@@ -291,6 +306,10 @@ int ta_trainer_init_random(ta_trainer* tr, unsigned long long seed, float std);
  *   "l<i>.cache.<x_normed|Q|K|V|attn_out|r_in|r_mid>" "cache.dx_attn_in" (last micro-batch, layer 0)
  * dtype: 0 = FP32, 1 = BF16. pitch is the row pitch in elements. */
 int ta_trainer_tensor(ta_trainer* tr, const char* name, void** dev_ptr, long* rows, long* cols, long* pitch, int* dtype);
+/* Switches of the step's fusions, for A/B comparisons: "fuse_swiglu" (1: SwiGLU forward / backward run inside the
+ * gate-up and down-dX GEMM epilogues; default 0: separate silu_mul kernels as the reference has them, which is the
+ * faster arrangement with the current tile shapes).  No reference counterpart. */
+int ta_trainer_set_option(ta_trainer* tr, const char* name, int value);
 /* Re-derive the BF16 working copies from the FP32 masters (after masters were uploaded). */
 int ta_trainer_sync_working(ta_trainer* tr);
 /* AdapterModel::zero_grad (adapter_model.cu:222-229): one memset of the flat gradient array. */

@@ -64,6 +64,9 @@ _PROTOS = {
     "ta_cast_bf16_to_f32": (c_int, [P, P, P, c_long, P]),
     "ta_cast_f32_to_bf16": (c_int, [P, P, P, c_long, P]),
     "ta_gemm_bf16": (c_int, [P, c_int, c_int, c_int, c_float, P, c_long, c_int, P, c_long, c_int, P, P, P, c_long, P]),
+    "ta_swiglu_proj_fwd": (c_int, [P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_float, P]),
+    "ta_swiglu_down_bwd": (c_int, [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, P]),
+    "ta_trainer_set_option": (c_int, [P, c_char_p, c_int]),
     "ta_lora_linear_fwd": (c_int, [P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_float, P]),
     "ta_lora_linear_bwd": (c_int, [P, P, P, P, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_float, P]),
     "ta_flash_attn_fwd": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),

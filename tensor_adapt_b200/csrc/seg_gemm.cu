@@ -37,6 +37,14 @@ struct alignas(64) SegGemmParams {
     float* ws;
     long ws_split_stride;
     int* status;
+    // fused SwiGLU (see GemmOut::epi): `dual` tiles hold 128 gate columns and the 128 matching up columns
+    CUtensorMap tmB2[kMaxSegments];   // dual: the "up" operand of each segment (up_w, or the up adapter's B)
+    int k_half[kMaxSegments];         // dual rank-r segment: A columns [0,k_half) feed the gate half, [k_half,2k_half) the up half
+    int dual, epi;
+    void* C2;                         // epi 1: up output; epi 2: d_up output
+    void* C3;                         // epi 1: act output
+    const __nv_bfloat16* gate_in;     // epi 2: forward gate / up activations
+    const __nv_bfloat16* up_in;
 };
 
 constexpr int BM = 128;       // rows of one MMA / one TMEM accumulator
@@ -59,7 +67,7 @@ struct Cfg {
     static constexpr int STAGES = MH == 2 ? 3 : (BN >= 224) ? 4 : (BN == 128) ? 6 : 8;
     static constexpr uint32_t TMEM_COLS = MH == 2 ? 512 : pow2_at_least(2 * BN);
     static constexpr int NCHUNK_B = (BN + 63) / 64;
-    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 16384;   // ring, alignment slack, barriers, epilogue staging
 };
 
 struct TileCoord {
@@ -81,11 +89,66 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
     return t;
 }
 
+__device__ __forceinline__ uint4 pack8_bf16(const float (&o)[8]) {
+    uint4 w;
+    w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]); w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+    return w;
+}
+__device__ __forceinline__ void unpack8_bf16(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 t = unpack_bf16x2(w[i]);
+        f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+}
+// ── coalesced epilogue traffic through a per-warp staging tile ───────────────
+// tcgen05.ld hands every thread one ROW of the accumulator, so a direct store has 32 lanes writing 16 bytes to 32
+// different lines - one line per cycle in the load/store unit, which made the epilogue four times longer than its
+// bytes warrant.  Instead each warp owns a 32-row x 64-byte staging tile in shared memory (32 BF16 columns): threads
+// write their row's four 16-byte pieces (XOR-swizzled by row pair: conflict-free both ways), and the warp then moves
+// the tile with 4 lanes per row, 8 rows per instruction - full 32-byte sectors, a quarter of the line operations.
+// Loads of row-distributed inputs (residual, the forward's gate / up) go the same way in reverse.
+constexpr uint32_t kEpiStageBytes = 8 * 2048;   // eight epilogue warps
+
+__device__ __forceinline__ int stage_slot(int r, int piece) { return r * 4 + (piece ^ ((r >> 1) & 3)); }
+
+// thread `lane` has put its row's pieces at stage[stage_slot(lane, 0..3)]; writes the 32 x 32 tile to dst
+__device__ __forceinline__ void stage_store_tile(const uint4* stage, int lane, __nv_bfloat16* dst, long ld, int row0, int col0,
+                                                 int M, int N) {
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = i * 8 + (lane >> 2), pc = lane & 3;
+        const int grow = row0 + r, gcol = col0 + pc * 8;
+        if (grow < M && gcol < N) *reinterpret_cast<uint4*>(dst + size_t(grow) * ld + gcol) = stage[stage_slot(r, pc)];
+    }
+    __syncwarp();
+}
+
+// the reverse: the 32 x 32 tile of src lands in `mine[0..3]`, the four pieces of this thread's row (zeros outside)
+__device__ __forceinline__ void stage_load_rows(uint4* stage, int lane, const __nv_bfloat16* src, long ld, int row0, int col0, int M,
+                                                int N, uint4 (&mine)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = i * 8 + (lane >> 2), pc = lane & 3;
+        const int grow = row0 + r, gcol = col0 + pc * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (grow < M && gcol < N) v = *reinterpret_cast<const uint4*>(src + size_t(grow) * ld + gcol);
+        stage[stage_slot(r, pc)] = v;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < 4; g++) mine[g] = stage[stage_slot(lane, g)];
+    __syncwarp();
+}
+
 // Drains columns [c_lo*CW, c_hi*CW) of one 128-row accumulator: TMEM -> registers -> alpha, bias, residual
 // -> BF16 / FP32 store (or split-K partial).  `row` is the global output row of this thread's TMEM lane.
 template <int CW>
 __device__ __forceinline__ void epilogue_chunks(const SegGemmParams& p, uint32_t taddr, int row, bool row_ok, int n0,
-                                                int split, int c_lo, int c_hi) {
+                                                int split, int c_lo, int c_hi, uint4* stage) {
+    const int lane = threadIdx.x & 31;
 #pragma unroll 1
     for (int c = c_lo; c < c_hi; c++) {
         const int col0 = n0 + c * CW;
@@ -103,6 +166,34 @@ __device__ __forceinline__ void epilogue_chunks(const SegGemmParams& p, uint32_t
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+        }
+        if constexpr (CW == 32) {
+            if (!p.f32) {   // BF16 output: bias / residual / store through the staging tile (whole warp takes part)
+                uint4 res[4];
+                if (p.residual) stage_load_rows(stage, lane, p.residual, p.ldc, row - lane, col0, p.M, p.N, res);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const int col = col0 + g * 8;
+                    float o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) o[i] = v[g * 8 + i] * p.alpha;
+                    if (p.bias && col < p.N) {
+                        float b[8];
+                        unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
+#pragma unroll
+                        for (int i = 0; i < 8; i++) o[i] += b[i];
+                    }
+                    if (p.residual) {
+                        float r8[8];
+                        unpack8_bf16(res[g], r8);
+#pragma unroll
+                        for (int i = 0; i < 8; i++) o[i] += r8[i];
+                    }
+                    stage[stage_slot(lane, g)] = pack8_bf16(o);
+                }
+                stage_store_tile(stage, lane, reinterpret_cast<__nv_bfloat16*>(p.C), p.ldc, row - lane, col0, p.M, p.N);
+                continue;
+            }
         }
         if (!row_ok) continue;
 #pragma unroll
@@ -159,6 +250,98 @@ __device__ __forceinline__ void epilogue_chunks(const SegGemmParams& p, uint32_t
     }
 }
 
+__device__ __forceinline__ float bf16_round_f(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+// Fused SwiGLU forward epilogue of a dual tile: accumulator columns [0,128) are gate columns n0g.., columns
+// [128,256) the matching up columns.  Stores gate, up (both rounded to BF16 first, as ops::silu_mul_fwd reads them,
+// src/backend/cuda/ops.cu:913-923) and act = silu(gate) * up, each through the staging tile.  Chunks of 32 gate
+// columns [c_lo, c_hi).
+__device__ __forceinline__ void epilogue_swiglu_fwd(const SegGemmParams& p, uint32_t taddr, int row, int n0g, int c_lo, int c_hi,
+                                                    uint4* stage) {
+    const int lane = threadIdx.x & 31, row0 = row - lane;
+#pragma unroll 1
+    for (int c = c_lo; c < c_hi; c++) {
+        const int col0 = n0g + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t rg[32], ru[32];
+        tmem_ld_x32(taddr + c * 32, rg);
+        tmem_ld_x32(taddr + 128 + c * 32, ru);
+        tmem_ld_wait();
+        uint4 pa[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            float og[8], oa[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                og[i] = bf16_round_f(__uint_as_float(rg[g * 8 + i]) * p.alpha);
+                const float ou = bf16_round_f(__uint_as_float(ru[g * 8 + i]) * p.alpha);
+                oa[i] = __fdividef(og[i], 1.f + __expf(-og[i])) * ou;
+            }
+            stage[stage_slot(lane, g)] = pack8_bf16(og);
+            pa[g] = pack8_bf16(oa);
+        }
+        stage_store_tile(stage, lane, reinterpret_cast<__nv_bfloat16*>(p.C), p.ldc, row0, col0, p.M, p.N);
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            float ou[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) ou[i] = __uint_as_float(ru[g * 8 + i]) * p.alpha;
+            stage[stage_slot(lane, g)] = pack8_bf16(ou);
+        }
+        stage_store_tile(stage, lane, reinterpret_cast<__nv_bfloat16*>(p.C2), p.ldc, row0, col0, p.M, p.N);
+#pragma unroll
+        for (int g = 0; g < 4; g++) stage[stage_slot(lane, g)] = pa[g];
+        stage_store_tile(stage, lane, reinterpret_cast<__nv_bfloat16*>(p.C3), p.ldc, row0, col0, p.M, p.N);
+    }
+}
+
+// Fused SwiGLU backward epilogue: the accumulator is d_act; d_gate = d_act * up * silu'(gate), d_up = d_act * silu(gate)
+// (src/backend/cuda/ops.cu:925-941) with the forward's gate / up fetched through the staging tile (coalesced).
+__device__ __forceinline__ void epilogue_swiglu_bwd(const SegGemmParams& p, uint32_t taddr, int row, int n0, int c_lo, int c_hi,
+                                                    uint4* stage) {
+    const int lane = threadIdx.x & 31, row0 = row - lane;
+#pragma unroll 1
+    for (int c = c_lo; c < c_hi; c++) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        uint4 gq[4], uq[4];
+        stage_load_rows(stage, lane, p.gate_in, p.ldc, row0, col0, p.M, p.N, gq);
+        stage_load_rows(stage, lane, p.up_in, p.ldc, row0, col0, p.M, p.N, uq);
+        uint32_t r[32];
+        tmem_ld_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        uint4 pu[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            float gt[8], up[8], dg[8], du[8];
+            unpack8_bf16(gq[g], gt);
+            unpack8_bf16(uq[g], up);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float d = __uint_as_float(r[g * 8 + i]) * p.alpha;
+                const float sig = __fdividef(1.f, 1.f + __expf(-gt[i]));
+                dg[i] = d * up[i] * (sig * (1.f + gt[i] * (1.f - sig)));
+                du[i] = d * (gt[i] * sig);
+            }
+            stage[stage_slot(lane, g)] = pack8_bf16(dg);
+            pu[g] = pack8_bf16(du);
+        }
+        stage_store_tile(stage, lane, reinterpret_cast<__nv_bfloat16*>(p.C), p.ldc, row0, col0, p.M, p.N);
+#pragma unroll
+        for (int g = 0; g < 4; g++) stage[stage_slot(lane, g)] = pu[g];
+        stage_store_tile(stage, lane, reinterpret_cast<__nv_bfloat16*>(p.C2), p.ldc, row0, col0, p.M, p.N);
+    }
+}
+
+// Which half (0 = gate, 1 = up) the 16-column MMA step at A column `c` of a dual rank-r segment feeds, and the byte
+// offset of its B operand inside that half's shared-memory tile (whose first column is B column `up_k0` for the up half).
+struct DualStep { int half; uint32_t b_off; };
+__device__ __forceinline__ DualStep dual_step(int c, int k_half, int kb) {
+    if (c < k_half) return DualStep{0, uint32_t(c - kb * BK) * 2u};
+    const int up_k0 = max(kb * BK - k_half, 0);
+    return DualStep{1, uint32_t(c - k_half - up_k0) * 2u};
+}
+
 template <int BN, int MH>
 __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_constant__ SegGemmParams p) {
     using C = Cfg<BN, MH>;
@@ -170,6 +353,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // per-warp epilogue staging tile (2 KB each) behind the barrier block; warps 2..9 are the epilogue warps
+    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES + 256) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 128 : 0);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -196,7 +381,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
     const uint32_t tmem_base = *tmem_slot;
 
     const int m_tiles = (p.M + C::TILE_M - 1) / C::TILE_M;
-    const int n_tiles = (p.N + BN - 1) / BN;
+    const int tile_n = (MH == 2 && BN == 256 && p.dual) ? 128 : BN;   // output columns (of gate) one tile covers
+    const int n_tiles = (p.N + tile_n - 1) / tile_n;
     const int total = m_tiles * n_tiles * p.split_k;
 
     if (warp == 0) {
@@ -204,10 +390,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
             for (int s = 0; s < p.nseg; s++) {
                 prefetch_tensormap(&p.tmA[s]);
                 prefetch_tensormap(&p.tmB[s]);
+                if (p.dual) prefetch_tensormap(&p.tmB2[s]);
             }
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, BN);
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n);
                 for (int s = 0; s < p.nseg; s++) {
                     const int nkb = (p.K[s] + BK - 1) / BK;
                     int kb_lo = 0, kb_hi = nkb;
@@ -230,6 +417,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
                             tma_load_2d(sa, &p.tmA[s], &full[stage], tc.m0, kb * BK);
                             tma_load_2d(sa + 8192, &p.tmA[s], &full[stage], tc.m0 + 64, kb * BK);
                         }
+                        if constexpr (MH == 2 && BN == 256) {
+                            if (p.dual) {   // two boxes {64, 128}: gate rows, then the matching up rows (K-major only)
+                                tma_load_2d(sb, &p.tmB[s], &full[stage], kb * BK, tc.n0);
+                                tma_load_2d(sb + 16384, &p.tmB2[s], &full[stage],
+                                            p.k_half[s] ? max(kb * BK - p.k_half[s], 0) : kb * BK, tc.n0);
+                                continue;
+                            }
+                        }
                         if (!b_mn) {
                             tma_load_2d(sb, &p.tmB[s], &full[stage], kb * BK, tc.n0);
                         } else {
@@ -245,7 +440,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
         if (lane == 0) {
             uint32_t it = 0, lt = 0;
             for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, BN);
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n);
                 const uint32_t buf = MH == 2 ? 0u : (lt & 1u);
                 const uint32_t use = MH == 2 ? lt : (lt >> 1);
                 if (!mbar_wait(&tempty[buf], (use & 1u) ^ 1u, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
@@ -270,6 +465,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
                         const uint32_t sb = sa + C::A_BYTES;
                         const int krem = p.K[s] - kb * BK;
                         const int kinstr = krem >= BK ? 4 : (krem + 15) / 16;
+                        if (MH == 2 && BN == 256 && p.dual && p.k_half[s]) {
+                            // rank-r segment of a dual tile: each 16-column step feeds one half (N = 128) of the tile;
+                            // the first step of each half starts that half's accumulation if nothing came before
+                            const uint32_t idesc_h = umma_idesc_bf16(BM, 128, false, false);
+                            for (int ki = 0; ki < kinstr; ki++) {
+                                const DualStep ds = dual_step(kb * BK + ki * 16, p.k_half[s], kb);
+                                const uint64_t bd = smem_desc_sw128(sb + ds.half * 16384 + ds.b_off, 16, 1024);
+#pragma unroll
+                                for (int hh = 0; hh < MH; hh++)
+                                    umma_bf16(d_tmem + hh * 256 + ds.half * 128, smem_desc_sw128(sa + hh * 16384 + ki * 32, 16, 1024),
+                                              bd, idesc_h, acc);
+                            }
+                            umma_commit(&empty[stage]);
+                            continue;
+                        }
                         for (int ki = 0; ki < kinstr; ki++) {
                             const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
                                                      : smem_desc_sw128(sb + ki * 32, 16, 1024);
@@ -295,7 +505,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
         const int eh = (warp - 2) >> 2;
         uint32_t lt = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
-            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, BN);
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n);
             const uint32_t buf = MH == 2 ? 0u : (lt & 1u);
             const uint32_t use = MH == 2 ? lt : (lt >> 1);
             if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
@@ -309,7 +519,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
                 const int row = tc.m0 + hh * BM + lg * 32 + lane;
                 const bool row_ok = row < p.M;
                 const uint32_t taddr = tmem_base + (MH == 2 ? uint32_t(hh) * 256u : buf * BN) + (uint32_t(lg * 32) << 16);
-                epilogue_chunks<CW>(p, taddr, row, row_ok, tc.n0, tc.split, c_lo, c_hi);
+                if constexpr (CW == 32) {
+                    if (p.epi == 1) { if constexpr (MH == 2 && BN == 256) epilogue_swiglu_fwd(p, taddr, row, tc.n0, 0, 4, stage); continue; }
+                    if (p.epi == 2) { epilogue_swiglu_bwd(p, taddr, row, tc.n0, c_lo, c_hi, stage); continue; }
+                }
+                epilogue_chunks<CW>(p, taddr, row, row_ok, tc.n0, tc.split, c_lo, c_hi, stage);
             }
             tcgen05_fence_before_sync();
             __syncwarp();
@@ -348,7 +562,7 @@ struct PairCfg {
     static constexpr uint32_t A_BYTES = 256 * BK * 2;
     static constexpr uint32_t B_BYTES = 128 * BK * 2;              // half tile (BN/2 <= 128 rows, or two 64-column chunks)
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 16384;
 };
 
 template <int BN>
@@ -364,6 +578,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     uint64_t* tempty = tfull + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // per-warp epilogue staging tile (2 KB each) behind the barrier block; warps 2..9 are the epilogue warps
+    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES + 256) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 128 : 0);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -474,7 +690,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             tcgen05_fence_after_sync();
             const int row = tc.m0 + int(rank) * 256 + eh * BM + lg * 32 + lane;
             const uint32_t taddr = tmem_base + uint32_t(eh) * 256u + (uint32_t(lg * 32) << 16);
-            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, 0, BN / 32);
+            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, 0, BN / 32, stage);
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0);
@@ -512,7 +728,7 @@ struct Pair2Cfg {
     static constexpr uint32_t A_BYTES = 128 * BK * 2;
     static constexpr uint32_t B_BYTES = 128 * BK * 2;              // half tile: BN/2 <= 128 rows, or two 64-column chunks
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 16384;
 };
 
 template <int BN>
@@ -528,6 +744,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // per-warp epilogue staging tile (2 KB each) behind the barrier block; warps 2..9 are the epilogue warps
+    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES + 256) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 128 : 0);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -557,7 +775,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const uint32_t tmem_base = *tmem_slot;
 
     const int m_tiles = (p.M + 255) / 256;
-    const int n_tiles = (p.N + BN - 1) / BN;
+    const int tile_n = p.dual ? 128 : BN;     // dual tiles: 128 gate columns + the 128 matching up columns
+    const int n_tiles = (p.N + tile_n - 1) / tile_n;
     const int total = m_tiles * n_tiles;
 
     if (warp == 0) {
@@ -565,10 +784,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             for (int s = 0; s < p.nseg; s++) {
                 prefetch_tensormap(&p.tmA[s]);
                 prefetch_tensormap(&p.tmB[s]);
+                if (p.dual) prefetch_tensormap(&p.tmB2[s]);
             }
             uint32_t it = 0;
             for (int tile = pair; tile < total; tile += npairs) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, BN);
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, tile_n);
                 const int m0 = tc.m0 + int(rank) * 128, nh = tc.n0 + int(rank) * HALF;
                 for (int s = 0; s < p.nseg; s++) {
                     const int nkb = (p.K[s] + BK - 1) / BK;
@@ -582,6 +802,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         const uint32_t fbar = map_to_cta(smem_u32(&full[stage]), 0);
                         mbar_arrive_expect_tx_cluster(fbar, C::STAGE_BYTES);
                         tma_load_2d_pair(sa, &p.tmA[s], fbar, kb * BK, m0);             // box {64, 128}
+                        if (p.dual) {
+                            if (!p.k_half[s]) {
+                                // main segment: this CTA supplies one half of the N = 256 operand - rank 0 the gate rows,
+                                // rank 1 the matching up rows (box {64, 128} of its own tensor map)
+                                tma_load_2d_pair(sb, rank ? &p.tmB2[s] : &p.tmB[s], fbar, kb * BK, tc.n0);
+                            } else {
+                                // rank-r segment: two N = 128 products, each CTA supplies 64 rows of both (boxes {64, 64})
+                                tma_load_2d_pair(sb, &p.tmB[s], fbar, kb * BK, tc.n0 + int(rank) * 64);
+                                tma_load_2d_pair(sb + 8192, &p.tmB2[s], fbar, max(kb * BK - p.k_half[s], 0), tc.n0 + int(rank) * 64);
+                            }
+                            continue;
+                        }
                         if (!b_mn) {
                             tma_load_2d_pair(sb, &p.tmB[s], fbar, kb * BK, nh);         // box {64, 128}
                         } else {
@@ -615,11 +847,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         const uint32_t sb = sa + C::A_BYTES;
                         const int krem = p.K[s] - kb * BK;
                         const int kinstr = krem >= BK ? 4 : (krem + 15) / 16;
-                        for (int ki = 0; ki < kinstr; ki++) {
-                            const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
-                                                     : smem_desc_sw128(sb + ki * 32, 16, 1024);
-                            umma_bf16_pair(d_tmem, smem_desc_sw128(sa + ki * 32, 16, 1024), bd, idesc, acc);
-                            acc = 1;
+                        if (p.dual && p.k_half[s]) {
+                            const uint32_t idesc_h = umma_idesc_bf16(256, 128, false, false);
+                            for (int ki = 0; ki < kinstr; ki++) {
+                                const DualStep ds = dual_step(kb * BK + ki * 16, p.k_half[s], kb);
+                                umma_bf16_pair(d_tmem + ds.half * 128, smem_desc_sw128(sa + ki * 32, 16, 1024),
+                                               smem_desc_sw128(sb + ds.half * 8192 + ds.b_off, 16, 1024), idesc_h, acc);
+                            }
+                        } else {
+                            for (int ki = 0; ki < kinstr; ki++) {
+                                const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
+                                                         : smem_desc_sw128(sb + ki * 32, 16, 1024);
+                                umma_bf16_pair(d_tmem, smem_desc_sw128(sa + ki * 32, 16, 1024), bd, idesc, acc);
+                                acc = 1;
+                            }
                         }
                         umma_commit_pair(smem_u32(&empty[stage]));
                         umma_commit_pair(peer_empty0 + stage * 8);
@@ -638,13 +879,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         const int c_lo = eh * ((NCH + 1) / 2), c_hi = eh == 0 ? (NCH + 1) / 2 : NCH;
         uint32_t lt = 0;
         for (int tile = pair; tile < total; tile += npairs, lt++) {
-            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, BN);
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, tile_n);
             const uint32_t buf = lt & 1u, use = lt >> 1;
             if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
             tcgen05_fence_after_sync();
             const int row = tc.m0 + int(rank) * 128 + lg * 32 + lane;
             const uint32_t taddr = tmem_base + buf * 256u + (uint32_t(lg * 32) << 16);
-            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, c_lo, c_hi);
+            if (p.epi == 1)      epilogue_swiglu_fwd(p, taddr, row, tc.n0, eh * 2, eh * 2 + 2, stage);
+            else if (p.epi == 2) epilogue_swiglu_bwd(p, taddr, row, tc.n0, c_lo, c_hi, stage);
+            else                 epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, c_lo, c_hi, stage);
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0 + buf * 8);
@@ -791,6 +1034,8 @@ size_t tokens_gemm_ws_bytes_max(const ta_ctx* ctx, int M, int N) {
     return size_t(smax) * M * N * sizeof(float);
 }
 
+bool seg_gemm_supports_swiglu(const ta_ctx* ctx, int M) { return ctx && M >= 256; }
+
 int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* segs, int nseg, const GemmOut& out) {
     if (!ctx) return TA_ERR_INVALID;
     if (nseg < 1 || nseg > kMaxSegments) return fail(ctx, TA_ERR_INVALID, "seg_gemm: 1..6 segments");
@@ -808,12 +1053,30 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     double ksum_all = 0;
     bool any_a_mn = false;
     for (int s = 0; s < nseg; s++) { ksum_all += segs[s].K; any_a_mn = any_a_mn || segs[s].a_mn; }
-    const TileChoice tcfg = out.split_k > 1 ? TileChoice{pick_bn(N), 1} : pick_tile(ctx, M, N, ksum_all, any_a_mn);
+    const bool dual = out.epi == 1;
+    if (out.epi < 0 || out.epi > 2) return fail(ctx, TA_ERR_INVALID, "seg_gemm: unknown epilogue");
+    if (out.epi) {
+        if (out.f32 || out.bias || out.residual || out.split_k > 1 || !out.C2 || (reinterpret_cast<uintptr_t>(out.C2) & 15))
+            return fail(ctx, TA_ERR_INVALID, "seg_gemm: fused SwiGLU takes plain BF16 outputs (C, C2) without bias / residual / split-K");
+        if (dual) {
+            if (!seg_gemm_supports_swiglu(ctx, M) || !out.C3 || (reinterpret_cast<uintptr_t>(out.C3) & 15) || segs[0].k_half)
+                return fail(ctx, TA_ERR_INVALID, "seg_gemm: fused gate/up needs M >= 256, an act output and a full-K first segment");
+            for (int s = 0; s < nseg; s++)
+                if (!segs[s].B2 || segs[s].a_mn || segs[s].b_mn || (segs[s].ldb2 % 8) || (reinterpret_cast<uintptr_t>(segs[s].B2) & 15) ||
+                    (segs[s].k_half && (segs[s].k_half % 16 || segs[s].K != 2 * segs[s].k_half)))
+                    return fail(ctx, TA_ERR_INVALID, "seg_gemm: fused gate/up segments are K-major pairs (B, B2); rank-r ones have K = 2 * k_half");
+        } else if (!out.gate_in || !out.up_in || (reinterpret_cast<uintptr_t>(out.gate_in) & 15) || (reinterpret_cast<uintptr_t>(out.up_in) & 15)) {
+            return fail(ctx, TA_ERR_INVALID, "seg_gemm: the SwiGLU backward epilogue needs the forward's gate and up");
+        }
+    }
+    const TileChoice tcfg = dual              ? TileChoice{256, 2}
+                            : out.split_k > 1 ? TileChoice{pick_bn(N), 1}
+                                              : pick_tile(ctx, M, N, dual ? 2 * ksum_all : ksum_all, any_a_mn);
     const int bn = tcfg.bn, tile_m = 128 * tcfg.mh;
     // CTA-pair kernel (512 x 256 tiles over two SMs): same A boxes as the 256-row kernel, half-width B boxes.
     // Opt-in (ta_ctx_set_gemm_tuning): measured 3-7 % slower than the single-CTA 256-row kernel on the 7B shapes.
     const bool use_pair2 = ctx->gemm_pair == 2 && bn == 256 && tcfg.mh == 2 && out.split_k <= 1 && M >= 256 && (ctx->sm_count % 2) == 0;
-    const bool use_pair = ctx->gemm_pair == 1 && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
+    const bool use_pair = ctx->gemm_pair == 1 && out.epi == 0 && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
     SegGemmParams p;
     std::memset(&p, 0, sizeof(p));
     for (int s = 0; s < nseg; s++) {
@@ -828,7 +1091,14 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
         if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, uint32_t(use_pair2 ? 128 : tile_m), &p.tmA[s]);
         else         rc = get_tmap_bf16(ctx, g.A, uint64_t(M), uint64_t(g.K), uint64_t(g.lda) * 2, 64, 64, &p.tmA[s]);
         if (rc) return rc;
-        if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(use_pair || use_pair2 ? bn / 2 : bn), &p.tmB[s]);
+        if (dual) {
+            // gate / up operand pair: 128-row boxes (64-row ones for a rank-r segment on the CTA-pair kernel)
+            const uint64_t kb_dim = g.k_half ? uint64_t(g.k_half) : uint64_t(g.K);
+            const uint32_t box_rows = (g.k_half && use_pair2) ? 64u : 128u;
+            rc = get_tmap_bf16(ctx, g.B, kb_dim, uint64_t(N), uint64_t(g.ldb) * 2, 64, box_rows, &p.tmB[s]);
+            if (!rc) rc = get_tmap_bf16(ctx, g.B2, kb_dim, uint64_t(N), uint64_t(g.ldb2) * 2, 64, box_rows, &p.tmB2[s]);
+            p.k_half[s] = g.k_half;
+        } else if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(use_pair || use_pair2 ? bn / 2 : bn), &p.tmB[s]);
         else         rc = get_tmap_bf16(ctx, g.B, uint64_t(N), uint64_t(g.K), uint64_t(g.ldb) * 2, 64, 64, &p.tmB[s]);
         if (rc) return rc;
         p.K[s] = g.K;
@@ -839,8 +1109,9 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     p.C = out.C; p.ldc = out.ldc; p.f32 = out.f32; p.accumulate = out.accumulate; p.alpha = out.alpha;
     p.bias = out.bias; p.residual = out.residual; p.status = ctx->d_status;
     p.split_k = 1; p.kb_per_split = 0;
+    p.dual = dual; p.epi = out.epi; p.C2 = out.C2; p.C3 = out.C3; p.gate_in = out.gate_in; p.up_in = out.up_in;
 
-    const int m_tiles = (M + tile_m - 1) / tile_m, n_tiles = (N + bn - 1) / bn;
+    const int m_tiles = (M + tile_m - 1) / tile_m, n_tiles = dual ? (N + 127) / 128 : (N + bn - 1) / bn;
     if (out.split_k > 1) {
         const int nkb = (segs[0].K + BK - 1) / BK;
         const int splits = std::min(out.split_k, nkb);
@@ -860,6 +1131,10 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     const int total = m_tiles * n_tiles * p.split_k;
     double ksum = 0;
     for (int s = 0; s < nseg; s++) ksum += segs[s].K;
+    if (dual) {   // every segment produces N gate and N up columns; a rank-r segment contracts k_half per column
+        ksum = 0;
+        for (int s = 0; s < nseg; s++) ksum += 2.0 * (segs[s].k_half ? segs[s].k_half : segs[s].K);
+    }
     ProfScope prof(out.no_host_state ? nullptr : ctx, stream, bn >= 128 ? PROF_GEMM : PROF_GEMM_SKINNY, 2.0 * M * N * ksum);
     int rc;
     if (use_pair2) {

@@ -27,6 +27,11 @@ struct GemmSegment {
     long ldb = 0;
     bool b_mn = false;
     int K = 0;
+    // fused gate/up ("dual") launches only: the up half's operand ([N][K] K-major, same pitch rules), and for a rank-r
+    // segment the rank: A is then [M][2*k_half] = [h_gate | h_up], B / B2 are the two adapters' [N][k_half]
+    const __nv_bfloat16* B2 = nullptr;
+    long ldb2 = 0;
+    int k_half = 0;
 };
 
 struct GemmOut {
@@ -42,7 +47,18 @@ struct GemmOut {
     float* split_ws = nullptr;          // split-K partials go here instead of the context workspace
     size_t split_ws_bytes = 0;
     bool no_host_state = false;         // encode tensor maps on the stack: no cache insert, no profiling events
+    // Fused SwiGLU.  epi 1 ("dual" launch, every segment carries B2): N counts the GATE columns; a tile computes 128 gate
+    // and the 128 matching up columns and stores gate -> C, up -> C2, act = silu(gate)*up -> C3 (all [M][ldc] BF16).
+    // epi 2: the product is d_act; with the forward's gate_in / up_in it stores d_gate -> C and d_up -> C2 instead.
+    int epi = 0;
+    void* C2 = nullptr;
+    void* C3 = nullptr;
+    const __nv_bfloat16* gate_in = nullptr;
+    const __nv_bfloat16* up_in = nullptr;
 };
+
+// Whether seg_gemm can run the fused SwiGLU forms for this many rows (they need the 256-row tile kernels).
+bool seg_gemm_supports_swiglu(const ta_ctx* ctx, int M);
 
 // Split count the token-contracted gradient GEMM (M x N output, K tokens) should use, and the bytes
 // of partials that many splits need.

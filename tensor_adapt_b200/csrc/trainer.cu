@@ -130,12 +130,38 @@ int proj_fwd(ta_trainer* t, int l, int tgt, const bf16* x, const bf16* W, const 
     return seg_gemm(t->ctx, t->stream, BT, out, seg, nseg, o);
 }
 
+// gate = x.Wg^T (+LoRA), up = x.Wu^T (+LoRA), act = silu(gate)*up as ONE launch: every tile computes 128 gate columns and
+// the 128 matching up columns and the epilogue stores all three (proj_fwd x 2 + ops::silu_mul_fwd, qwen2.cu:137-147).
+// Needs h_s of both adapters as one [BT][2r] buffer (lora_down_group) when they are on.
+int proj_gate_up_swiglu(ta_trainer* t, int l, const bf16* x, int BT) {
+    const int H = t->mc.hidden, I = t->mc.intermediate;
+    LayerW& w = t->L[l];
+    LayerCache& k = t->cache[l];
+    GemmSegment seg[2];
+    seg[0].A = x; seg[0].lda = H; seg[0].K = H;
+    seg[0].B = w.gate_w; seg[0].ldb = H; seg[0].B2 = w.up_w; seg[0].ldb2 = H;
+    int nseg = 1;
+    LoraRef lg = t->ref(l, T_GATE), lu = t->ref(l, T_UP);
+    if (lg.on() && lu.on()) {
+        seg[1].A = k.h[T_GATE]; seg[1].lda = t->slot(l, T_GATE).h_ld; seg[1].K = 2 * lg.r; seg[1].k_half = lg.r;
+        seg[1].B = lg.B; seg[1].ldb = lg.r; seg[1].B2 = lu.B; seg[1].ldb2 = lu.r;
+        nseg = 2;
+    }
+    GemmOut o;
+    o.C = k.gate; o.C2 = k.up; o.C3 = k.act; o.ldc = I; o.epi = 1;
+    return seg_gemm(t->ctx, t->stream, BT, I, seg, nseg, o);
+}
+
 struct BwdProj { const bf16* dY; const bf16* W; int tgt; };
+// Optional fused SwiGLU backward on the product of a backward group (the down projection's dX = d_act): the epilogue
+// turns d_act into d_gate / d_up with the forward's gate / up and d_act itself is never stored.
+struct SwigluBwd { const bf16* gate = nullptr; const bf16* up = nullptr; bf16* d_gate = nullptr; bf16* d_up = nullptr; };
 
 // dX = sum_i dY_i.W_i + sum_i dh_i.A_i in ONE segmented GEMM; gA_i, gB_i accumulated on the way.
 // `fused`: the projections share x and form a fused group (contiguous A / gA blocks, dh slices of one
 // [BT][np*r] buffer), so gA of the whole group is one pass over x.
-int proj_bwd_group(ta_trainer* t, int l, const bf16* x, const BwdProj* ps, int np, bf16* dX, int BT, bool fused) {
+int proj_bwd_group(ta_trainer* t, int l, const bf16* x, const BwdProj* ps, int np, bf16* dX, int BT, bool fused,
+                   const SwigluBwd* swiglu = nullptr) {
     GemmSegment seg[kMaxSegments];
     int nseg = 0, in = 0;
     for (int i = 0; i < np; i++) {
@@ -183,6 +209,7 @@ int proj_bwd_group(ta_trainer* t, int l, const bf16* x, const BwdProj* ps, int n
     }
     GemmOut o;
     o.C = dX; o.ldc = in;
+    if (swiglu) { o.epi = 2; o.C = swiglu->d_gate; o.C2 = swiglu->d_up; o.gate_in = swiglu->gate; o.up_in = swiglu->up; }
     return seg_gemm(t->ctx, t->stream, BT, in, seg, nseg, o);
 }
 
@@ -195,6 +222,8 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count, bool exchange) {
     void* s = t->stream;
     const int BT = Bm * T, H = c.hidden, I = c.intermediate, qd = c.q_heads * c.head_dim, kv = c.kv_heads * c.head_dim;
     const int Lyr = c.layers;
+    // SwiGLU folded into the GEMM epilogues (no act / d_act round trips) whenever the 256-row tile kernels apply
+    const bool swiglu_fused = t->fuse_swiglu && seg_gemm_supports_swiglu(ctx, BT);
 
     // ── forward ────────────────────────────────────────────────────────────
     RC(ta_embed_fwd(ctx, t->embed, t->tok, t->cache[0].r_in, BT, H, s));
@@ -212,9 +241,13 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count, bool exchange) {
         RC(proj_fwd(t, l, T_O, k.attn_out, w.o_w, nullptr, k.r_in, k.r_mid, BT));          // + residual
         RC(ta_rms_norm_fwd(ctx, k.r_mid, w.post_norm, k.x_normed2, k.post_rms, BT, H, c.rms_eps, s));
         if (t->fuse_gu) RC(lora_down_group(t, l, T_GATE, 2, k.x_normed2, BT));
-        RC(proj_fwd(t, l, T_GATE, k.x_normed2, w.gate_w, nullptr, nullptr, k.gate, BT, t->fuse_gu));
-        RC(proj_fwd(t, l, T_UP, k.x_normed2, w.up_w, nullptr, nullptr, k.up, BT, t->fuse_gu));
-        RC(ta_silu_mul_fwd(ctx, k.gate, k.up, k.act, long(BT) * I, s));
+        if (swiglu_fused && (t->fuse_gu || (!t->ref(l, T_GATE).on() && !t->ref(l, T_UP).on()))) {
+            RC(proj_gate_up_swiglu(t, l, k.x_normed2, BT));
+        } else {
+            RC(proj_fwd(t, l, T_GATE, k.x_normed2, w.gate_w, nullptr, nullptr, k.gate, BT, t->fuse_gu));
+            RC(proj_fwd(t, l, T_UP, k.x_normed2, w.up_w, nullptr, nullptr, k.up, BT, t->fuse_gu));
+            RC(ta_silu_mul_fwd(ctx, k.gate, k.up, k.act, long(BT) * I, s));
+        }
         RC(proj_fwd(t, l, T_DOWN, k.act, w.down_w, nullptr, k.r_mid, r_next, BT));         // + residual
     }
     RC(ta_rms_norm_fwd(ctx, t->r_final, t->final_norm, t->x_final_normed, t->final_rms, BT, H, c.rms_eps, s));
@@ -232,11 +265,16 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count, bool exchange) {
     for (int l = Lyr - 1; l >= 0; l--) {
         LayerW& w = t->L[l];
         LayerCache& k = t->cache[l];
-        {   // FFN: dact = grad.Wd (+LoRA down)                                (qwen2.cu:221-225)
+        {   // FFN: dact = grad.Wd (+LoRA down), then dgate / dup                (qwen2.cu:221-230)
             BwdProj p{t->g_res, w.down_w, T_DOWN};
-            RC(proj_bwd_group(t, l, k.act, &p, 1, t->d_act, BT, false));
+            if (swiglu_fused) {
+                SwigluBwd sw; sw.gate = k.gate; sw.up = k.up; sw.d_gate = t->d_gate; sw.d_up = t->d_up;
+                RC(proj_bwd_group(t, l, k.act, &p, 1, nullptr, BT, false, &sw));
+            } else {
+                RC(proj_bwd_group(t, l, k.act, &p, 1, t->d_act, BT, false));
+                RC(ta_silu_mul_bwd(ctx, t->d_act, k.gate, k.up, t->d_gate, t->d_up, long(BT) * I, s));
+            }
         }
-        RC(ta_silu_mul_bwd(ctx, t->d_act, k.gate, k.up, t->d_gate, t->d_up, long(BT) * I, s));
         {   // dx_normed2 = dgate.Wg + dup.Wu (+LoRA)                           (:232-234)
             BwdProj p[2] = {{t->d_gate, w.gate_w, T_GATE}, {t->d_up, w.up_w, T_UP}};
             RC(proj_bwd_group(t, l, k.x_normed2, p, 2, t->d_xn, BT, t->fuse_gu));
@@ -573,6 +611,12 @@ int ta_trainer_tensor(ta_trainer* t, const char* name, void** dev_ptr, long* row
     if (pitch) *pitch = pt;
     if (dtype) *dtype = dt;
     return TA_OK;
+}
+
+int ta_trainer_set_option(ta_trainer* t, const char* name, int value) {
+    if (!t || !name) return TA_ERR_INVALID;
+    if (!std::strcmp(name, "fuse_swiglu")) { t->fuse_swiglu = value != 0; return TA_OK; }
+    return fail(t->ctx, TA_ERR_INVALID, std::string("trainer_set_option: unknown option ") + name);
 }
 
 int ta_trainer_sync_working(ta_trainer* t) {

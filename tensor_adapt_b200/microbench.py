@@ -117,6 +117,39 @@ def skinny(ctx, a):
     report("gA += dh^T.x", t, bytes_=2.0 * BT * (ind + r), shape=[ind, r, BT])
 
 
+def swiglu(ctx, a):
+    """The MLP's gate/up projection + SwiGLU and the down projection's dX + SwiGLU backward: separate kernels
+    against the launches that fold SwiGLU into the GEMM epilogue."""
+    BT, H, I = a.rows, a.D, a.I
+    x, Wg, Wu, Wd = rnd(BT, H), rnd(I, H, scale=0.02), rnd(I, H, scale=0.02), rnd(H, I, scale=0.02)
+    gate, up, act = (torch.empty(BT, I, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    dY = rnd(BT, H); d_act, d_gate, d_up = (torch.empty(BT, I, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    ctx.call("ta_ctx_set_gemm_tuning", 0, 0, a.pair)
+
+    def sep_f():
+        ctx.call("ta_gemm_bf16", BT, I, H, 1.0, ptr(x), H, 0, ptr(Wg), H, 0, None, None, ptr(gate), I, stream_ptr())
+        ctx.call("ta_gemm_bf16", BT, I, H, 1.0, ptr(x), H, 0, ptr(Wu), H, 0, None, None, ptr(up), I, stream_ptr())
+        ctx.call("ta_silu_mul_fwd", ptr(gate), ptr(up), ptr(act), BT * I, stream_ptr())
+
+    def fus_f():
+        ctx.call("ta_swiglu_proj_fwd", ptr(x), ptr(Wg), ptr(Wu), None, None, None, ptr(gate), ptr(up), ptr(act), BT, H, I, 0, 1.0,
+                 stream_ptr())
+
+    def sep_b():
+        ctx.call("ta_gemm_bf16", BT, I, H, 1.0, ptr(dY), H, 0, ptr(Wd), I, 1, None, None, ptr(d_act), I, stream_ptr())
+        ctx.call("ta_silu_mul_bwd", ptr(d_act), ptr(gate), ptr(up), ptr(d_gate), ptr(d_up), BT * I, stream_ptr())
+
+    def fus_b():
+        ctx.call("ta_swiglu_down_bwd", ptr(dY), ptr(Wd), None, None, ptr(gate), ptr(up), ptr(d_gate), ptr(d_up), BT, H, I, 0, stream_ptr())
+
+    fl = 2.0 * BT * I * H
+    report("gate + up GEMMs + silu_mul_fwd", timeit(sep_f, a.iters, a.warmup, a.flush), flops=2 * fl, shape=[BT, H, I], pair=a.pair)
+    report("fused gate/up SwiGLU forward", timeit(fus_f, a.iters, a.warmup, a.flush), flops=2 * fl, shape=[BT, H, I], pair=a.pair)
+    report("down dX GEMM + silu_mul_bwd", timeit(sep_b, a.iters, a.warmup, a.flush), flops=fl, shape=[BT, H, I], pair=a.pair)
+    report("fused down dX SwiGLU backward", timeit(fus_b, a.iters, a.warmup, a.flush), flops=fl, shape=[BT, H, I], pair=a.pair)
+    ctx.call("ta_ctx_set_gemm_tuning", 0, 0, 0)
+
+
 def kmeans(ctx, a):
     """Centroid merge (2048 vectors of dimension 512, k = 8 by default): reference-mode k-means and the seeded
     k-means++ / mass-ranked extension, whole call including its per-pass host synchronisation."""
@@ -165,7 +198,7 @@ def rowops(ctx, a):
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention", "gemm", "lora", "rowops", "skinny", "kmeans"):
+    for name in ("attention", "gemm", "lora", "rowops", "skinny", "kmeans", "swiglu"):
         s = sub.add_parser(name)
         s.add_argument("--iters", type=int, default=10); s.add_argument("--warmup", type=int, default=3)
         s.add_argument("--flush", action="store_true")
@@ -187,9 +220,11 @@ def main():
         else:
             for k, v in (("rows", 16384), ("D", 3584), ("I", 18944)):
                 s.add_argument("--" + k, type=int, default=v)
+            if name == "swiglu":
+                s.add_argument("--pair", type=int, default=0)
     a = ap.parse_args()
     ctx = ta.Context(0)
-    {"attention": attention, "gemm": gemm, "lora": lora, "rowops": rowops, "skinny": skinny, "kmeans": kmeans}[a.what](ctx, a)
+    {"attention": attention, "gemm": gemm, "lora": lora, "rowops": rowops, "skinny": skinny, "kmeans": kmeans, "swiglu": swiglu}[a.what](ctx, a)
     torch.cuda.synchronize()
     ctx.check_device()
 
