@@ -10,7 +10,8 @@ import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_long, c_size_t, c_void_p
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libtensor_adapt_b200.so")
+# TENSOR_ADAPT_B200_LIB points at another build of the same library (e.g. an experimental one beside the installed one)
+LIB_PATH = os.environ.get("TENSOR_ADAPT_B200_LIB") or os.path.join(_PKG, "libtensor_adapt_b200.so")
 
 TA_OK = 0
 ERR_NAMES = {-1: "TA_ERR_INVALID", -2: "TA_ERR_CUDA", -3: "TA_ERR_UNSUPPORTED", -4: "TA_ERR_DEVICE_TIMEOUT",
