@@ -57,12 +57,16 @@ int ta_selftest_bounded_wait(ta_ctx* ctx, int limit_us, int* wait_returned_true,
 /* Kernels launched through this context so far. */
 long ta_launch_count(const ta_ctx* ctx);
 /* Experiment knob, no counterpart in the reference: force the GEMM tile (tile_n in {64,128,224,256},
- * tile_m_halves 1 = 128-row or 2 = 256-row tiles; 0,0 = the built-in cost model) and / or select the
- * CTA-pair kernel for 256-wide tiles.  Results are bit-identical for every choice.
+ * tile_m_halves 1 = 128-row or 2 = 256-row tiles; 0,0 = the built-in cost model) and / or select a
+ * CTA-pair kernel for 256-wide tiles (cta_pair 1: 512 x 256 pair tiles, 2: 256 x 256 with double-buffered accumulators).  Results are bit-identical for every choice.
  * Threading: a context, and every object created from it, belongs to ONE host thread at a time (the
  * reference's Device is single-threaded too); the library keeps per-device launch attributes and the
  * static-scratch address in unsynchronised process-wide state that is written on first use. */
 int ta_ctx_set_gemm_tuning(ta_ctx* ctx, int tile_n, int tile_m_halves, int cta_pair);
+/* Experiment knob, no counterpart in the reference: the order in which the persistent CTAs walk the output tiles
+ * (which operand panels a wave shares through L2): row groups of group_m tiles, inside column bands of group_n tiles
+ * (0, 0 = the built-in choice).  Results are identical for every order; only DRAM traffic and speed change. */
+int ta_ctx_set_gemm_raster(ta_ctx* ctx, int group_m, int group_n);
 /* Optional CUDA-event timing of the tensor-core kernels, off by default (it adds two event records
  * per launch). Classes: 0 = segmented GEMM with tiles >= 128 wide, 1 = skinny GEMMs (rank-r and
  * split-K), 2 = attention forward, 3 = attention backward. ta_profile_read synchronises the device

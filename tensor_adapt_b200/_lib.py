@@ -49,6 +49,7 @@ _PROTOS = {
     "ta_launch_count": (c_long, [P]),
     "ta_selftest_bounded_wait": (c_int, [P, c_int, POINTER(c_int), POINTER(c_int), P]),
     "ta_ctx_set_gemm_tuning": (c_int, [P, c_int, c_int, c_int]),
+    "ta_ctx_set_gemm_raster": (c_int, [P, c_int, c_int]),
     "ta_profile_enable": (c_int, [P, c_int]),
     "ta_profile_read": (c_int, [P, c_int, POINTER(c_long), POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
     "ta_rms_norm_fwd": (c_int, [P, P, P, P, P, c_int, c_int, c_float, P]),

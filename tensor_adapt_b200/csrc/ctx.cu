@@ -153,6 +153,13 @@ int ta_device_status(ta_ctx* ctx, int* status) {
     return TA_OK;
 }
 
+int ta_ctx_set_gemm_raster(ta_ctx* ctx, int group_m, int group_n) {
+    if (!ctx || group_m < 0 || group_n < 0) return TA_ERR_INVALID;
+    ctx->gemm_group_m = group_m;
+    ctx->gemm_group_n = group_n;
+    return TA_OK;
+}
+
 long ta_launch_count(const ta_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
 int ta_ctx_set_gemm_tuning(ta_ctx* ctx, int tile_n, int tile_m_halves, int cta_pair) {

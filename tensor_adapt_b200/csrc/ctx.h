@@ -49,6 +49,7 @@ struct ta_ctx {
     long launches = 0;              // kernels launched through this context (bench.py's gpu_launches)
     // GEMM tile overrides for experiments (ta_ctx_set_gemm_tuning); 0 = let the cost model choose
     int gemm_force_bn = 0, gemm_force_mh = 0;
+    int gemm_group_m = 0, gemm_group_n = 0;   // raster override (0 = built-in choice)
     int gemm_pair = 0;              // 256-wide tiles: 1 = CTA-pair kernel with 512 x 256 pair tiles, 2 = 256 x 256 pair tiles
     // optional per-kernel-class timing with CUDA events (off by default; see ta_profile_*)
     bool profiling = false;

@@ -41,6 +41,7 @@ struct alignas(64) SegGemmParams {
     CUtensorMap tmB2[kMaxSegments];   // dual: the "up" operand of each segment (up_w, or the up adapter's B)
     int k_half[kMaxSegments];         // dual rank-r segment: A columns [0,k_half) feed the gate half, [k_half,2k_half) the up half
     int dual, epi;
+    int group_m, group_n;             // raster (decode_tile)
     void* C2;                         // epi 1: up output; epi 2: d_up output
     void* C3;                         // epi 1: act output
     const __nv_bfloat16* gate_in;     // epi 2: forward gate / up activations
@@ -50,7 +51,7 @@ struct alignas(64) SegGemmParams {
 constexpr int BM = 128;       // rows of one MMA / one TMEM accumulator
 constexpr int BK = 64;
 constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, eight epilogue warps
-constexpr int GROUP_M = 16;   // m-tiles per raster group: a wave touches ~16 A tiles and ~9 B tiles -> L2 reuse
+constexpr int GROUP_M = 16;   // m-tiles per raster group when there are many n-tiles: a wave touches ~16 A and ~9 B panels
 
 constexpr uint32_t pow2_at_least(uint32_t v) { uint32_t p = 32; while (p < v) p <<= 1; return p; }
 
@@ -74,18 +75,29 @@ struct TileCoord {
     int m0, n0, split;
 };
 
-__device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_tiles, int bm, int bn) {
+// Tile order (what a wave of CTAs works on together decides what stays in L2): column bands of `group_n` n-tiles
+// outermost (0 = one band), inside a band row groups of `group_m` m-tiles, inside a group m fastest.  A row group's A
+// panel and a band's B panel are what consecutive waves re-use.
+__device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_tiles, int bm, int bn, int group_m, int group_n) {
     const int per_split = m_tiles * n_tiles;
     TileCoord t;
     t.split = tile / per_split;
     int rem = tile - t.split * per_split;
-    const int per_group = GROUP_M * n_tiles;
+    int n_first = 0, n_band = n_tiles;
+    if (group_n > 0 && group_n < n_tiles) {
+        const int per_band = m_tiles * group_n;
+        const int band = rem / per_band;
+        n_first = band * group_n;
+        n_band = min(group_n, n_tiles - n_first);
+        rem -= band * per_band;      // the last, narrower band keeps m_tiles * n_band tiles: rem stays in range
+    }
+    const int per_group = group_m * n_band;
     const int g = rem / per_group;
-    const int first_m = g * GROUP_M;
-    const int gsz = min(GROUP_M, m_tiles - first_m);
+    const int first_m = g * group_m;
+    const int gsz = min(group_m, m_tiles - first_m);
     const int in_g = rem - g * per_group;
     t.m0 = (first_m + in_g % gsz) * bm;
-    t.n0 = (in_g / gsz) * bn;
+    t.n0 = (n_first + in_g / gsz) * bn;
     return t;
 }
 
@@ -394,7 +406,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
             }
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n);
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n, p.group_m, p.group_n);
                 for (int s = 0; s < p.nseg; s++) {
                     const int nkb = (p.K[s] + BK - 1) / BK;
                     int kb_lo = 0, kb_hi = nkb;
@@ -440,7 +452,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
         if (lane == 0) {
             uint32_t it = 0, lt = 0;
             for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n);
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n, p.group_m, p.group_n);
                 const uint32_t buf = MH == 2 ? 0u : (lt & 1u);
                 const uint32_t use = MH == 2 ? lt : (lt >> 1);
                 if (!mbar_wait(&tempty[buf], (use & 1u) ^ 1u, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
@@ -505,7 +517,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
         const int eh = (warp - 2) >> 2;
         uint32_t lt = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
-            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n);
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, C::TILE_M, tile_n, p.group_m, p.group_n);
             const uint32_t buf = MH == 2 ? 0u : (lt & 1u);
             const uint32_t use = MH == 2 ? lt : (lt >> 1);
             if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
@@ -618,7 +630,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             }
             uint32_t it = 0;
             for (int tile = pair; tile < total; tile += npairs) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 512, BN);
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 512, BN, p.group_m, p.group_n);
                 const int m0 = tc.m0 + int(rank) * 256, nh = tc.n0 + int(rank) * HALF;
                 for (int s = 0; s < p.nseg; s++) {
                     const int nkb = (p.K[s] + BK - 1) / BK;
@@ -685,7 +697,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         const uint32_t tempty0 = map_to_cta(smem_u32(tempty), 0);
         uint32_t lt = 0;
         for (int tile = pair; tile < total; tile += npairs, lt++) {
-            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 512, BN);
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 512, BN, p.group_m, p.group_n);
             if (!mbar_wait(tfull, lt & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
             tcgen05_fence_after_sync();
             const int row = tc.m0 + int(rank) * 256 + eh * BM + lg * 32 + lane;
@@ -788,7 +800,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             }
             uint32_t it = 0;
             for (int tile = pair; tile < total; tile += npairs) {
-                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, tile_n);
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, tile_n, p.group_m, p.group_n);
                 const int m0 = tc.m0 + int(rank) * 128, nh = tc.n0 + int(rank) * HALF;
                 for (int s = 0; s < p.nseg; s++) {
                     const int nkb = (p.K[s] + BK - 1) / BK;
@@ -879,7 +891,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         const int c_lo = eh * ((NCH + 1) / 2), c_hi = eh == 0 ? (NCH + 1) / 2 : NCH;
         uint32_t lt = 0;
         for (int tile = pair; tile < total; tile += npairs, lt++) {
-            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, tile_n);
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, tile_n, p.group_m, p.group_n);
             const uint32_t buf = lt & 1u, use = lt >> 1;
             if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
             tcgen05_fence_after_sync();
@@ -1109,6 +1121,12 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     p.C = out.C; p.ldc = out.ldc; p.f32 = out.f32; p.accumulate = out.accumulate; p.alpha = out.alpha;
     p.bias = out.bias; p.residual = out.residual; p.status = ctx->d_status;
     p.split_k = 1; p.kb_per_split = 0;
+    // Raster.  Measured DRAM reads per launch on 16384-row problems (ncu, B200): with 74 n-tiles (N = 18944) groups of 16
+    // m-tiles are best (0.78-0.86 GB; 8: 1.25, 32: 2.0); with 16 n-tiles (N = 3584) a wave already spans all of N and
+    // narrow groups re-stream fewer A panels (K = 18944: 4 -> 1.80 GB, 8 -> 2.04, 16 -> 2.14, 64 -> 4.5; speed within noise).
+    // Column bands and L2 evict_first / evict_last hints on the operand loads were tried and raised traffic.
+    p.group_m = ctx->gemm_group_m > 0 ? ctx->gemm_group_m : ((dual ? (N + 127) / 128 : (N + bn - 1) / bn) <= 24 ? 4 : GROUP_M);
+    p.group_n = ctx->gemm_group_n;
     p.dual = dual; p.epi = out.epi; p.C2 = out.C2; p.C3 = out.C3; p.gate_in = out.gate_in; p.up_in = out.up_in;
 
     const int m_tiles = (M + tile_m - 1) / tile_m, n_tiles = dual ? (N + 127) / 128 : (N + bn - 1) / bn;

@@ -73,12 +73,16 @@ def gemm(ctx, a):
     C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     f = lambda: ctx.call("ta_gemm_bf16", M, N, K, 1.0, ptr(A), K, 0, ptr(Bm), Bm.shape[1], a.b_layout, None, None, ptr(C), N,
                          stream_ptr())
-    if a.tile:
-        bn, mh = (int(v) for v in a.tile.split(","))
+    if a.tile or a.pair:
+        bn, mh = (int(v) for v in a.tile.split(",")) if a.tile else (0, 0)
         ctx.call("ta_ctx_set_gemm_tuning", bn, mh, a.pair)
+    if a.raster:
+        gm, gn = (int(v) for v in a.raster.split(","))
+        ctx.call("ta_ctx_set_gemm_raster", gm, gn)
     report("gemm_bf16", timeit(f, a.iters, a.warmup, a.flush), flops=2.0 * M * N * K, shape=[M, N, K], b_layout=a.b_layout,
-           tile=a.tile or "auto", pair=a.pair)
+           tile=a.tile or "auto", pair=a.pair, raster=a.raster or "default")
     ctx.call("ta_ctx_set_gemm_tuning", 0, 0, 0)
+    ctx.call("ta_ctx_set_gemm_raster", 0, 0)
 
 
 def lora(ctx, a):
@@ -211,6 +215,7 @@ def main():
             s.add_argument("--b-layout", type=int, default=0)
             s.add_argument("--tile", default="", help='force a tile "BN,MH" (experiment knob)')
             s.add_argument("--pair", type=int, default=0, help="CTA-pair kernel: 0 off, 1 = 512x256 pair tiles, 2 = 256x256")
+            s.add_argument("--raster", default="", help='tile order "GROUP_M,GROUP_N" (experiment knob; 0 = default)')
         elif name == "kmeans":
             for k, v in (("N", 2048), ("D", 512), ("k", 8)):
                 s.add_argument("--" + k, type=int, default=v)
