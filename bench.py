@@ -59,9 +59,9 @@ SHAPES = {
 # `python -m tensor_adapt_b200.microbench gemm --M 16384 --N .. --K ..` (summary under profiles/), with the
 # launches of each shape per layer pass; `roofline.traffic` is their launch-weighted mean.
 NCU_GEMM_TRAFFIC_7B = {
-    "16384x18944x3584 (gate, up, dX of down)": (1.334e9, 3),
-    "16384x3584x18944 (down, halves of dX of gate+up)": (2.288e9, 3),
-    "16384x3584x3584 (q, o and their dX)": (0.369e9, 4),
+    "16384x18944x3584 (gate, up, dX of down)": (1.391e9, 3),
+    "16384x3584x18944 (down, halves of dX of gate+up)": (2.163e9, 3),
+    "16384x3584x3584 (q, o and their dX)": (0.278e9, 4),
 }
 
 
