@@ -293,17 +293,26 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ q, int Hq, __nv_bfloat16
         const int H = pass == 0 ? Hq : Hk;
         if (!base) continue;
         uint4* row = reinterpret_cast<uint4*>(base + size_t(bt) * H * hd);
-        for (int h = 0; h < H; h++) {
-            uint4 v = row[h * gpr + g];
-            float f[8];
-            unpack8(v, f);
+        // four heads per round: all four loads are issued before the first store (the rotation is in place, so the
+        // compiler cannot hoist a load over the previous head's store by itself)
+        for (int h0 = 0; h0 < H; h0 += 4) {
+            uint4 v[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float x0 = f[2 * j], x1 = f[2 * j + 1];
-                f[2 * j] = x0 * cs[j] - x1 * sn[j];
-                f[2 * j + 1] = x0 * sn[j] + x1 * cs[j];
+            for (int u = 0; u < 4; u++)
+                if (h0 + u < H) v[u] = row[(h0 + u) * gpr + g];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (h0 + u >= H) break;
+                float f[8];
+                unpack8(v[u], f);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float x0 = f[2 * j], x1 = f[2 * j + 1];
+                    f[2 * j] = x0 * cs[j] - x1 * sn[j];
+                    f[2 * j + 1] = x0 * sn[j] + x1 * cs[j];
+                }
+                row[(h0 + u) * gpr + g] = pack8(f);
             }
-            row[h * gpr + g] = pack8(f);
         }
     }
 }
