@@ -131,3 +131,21 @@ def test_reference_arm_of_bench_does_not_load_the_product_library():
     assert r.returncode == 0, r.stderr[-2000:]
     line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert line["impl"] == "reference" and ("unavailable" in line or line["value"] > 0)
+
+
+def test_shim_built_reference_tools_fail_loudly_without_a_gpu(tmp_path):
+    """The reference's unmodified tools linked on the shim have no CPU path either: without an sm_100 device they
+    exit with the reference's own error convention (message on stderr, exit code 1), they do not fall back."""
+    import struct
+    import subprocess
+    import torch
+    tool = os.path.join(ROOT, "oracle", "_ref", "shim", "centroid-merge")
+    if not os.path.exists(tool):
+        pytest.skip("shim tools not built (needs the reference checkout)")
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present; tests/test_gpu_shim_tools.py covers the tools")
+    d = tmp_path / "snaps"; d.mkdir()
+    for i in range(3):
+        (d / f"step-{i}.centroid").write_bytes(struct.pack("<i", 8) + np.arange(8, dtype="<f4").tobytes() + struct.pack("<f", 1.0))
+    r = subprocess.run([tool, str(d), "--out", str(tmp_path / "out.centroid"), "--clusters", "2"], capture_output=True, text=True)
+    assert r.returncode == 1 and "error:" in r.stderr and not (tmp_path / "out.centroid").exists()
