@@ -42,8 +42,11 @@ int encode_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1,
     cuuint64_t gstride[1] = {pitch_bytes};
     cuuint32_t box[2] = {box0, box1};
     cuuint32_t estr[2] = {1, 1};
+    // swizzle = the inner extent of the box: 64 elements (128 B) for the MMA operand tiles, 32 elements (64 B) for the
+    // 32 x 32 output tiles the GEMM epilogue stores
+    const CUtensorMapSwizzle swz = box0 >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : box0 == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         char buf[200];

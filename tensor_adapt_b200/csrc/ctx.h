@@ -79,8 +79,9 @@ namespace ta {
 int fail(ta_ctx* ctx, int code, const std::string& msg);
 int check_cuda(ta_ctx* ctx, cudaError_t e, const char* what);
 
-// Cached 2-D BF16 tensor map with 128-byte swizzle: tensor [dim1 rows][dim0 cols], row pitch in bytes,
-// box [box1 rows][box0 cols]; out-of-bounds elements read as zero.
+// Cached 2-D BF16 tensor map: tensor [dim1 rows][dim0 cols], row pitch in bytes, box [box1 rows][box0 cols], swizzle
+// matching the box's inner extent (128 B for 64 columns, 64 B for 32); out-of-bounds elements read as zero and are not
+// written by stores.
 int get_tmap_bf16(ta_ctx* ctx, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0,
                   uint32_t box1, CUtensorMap* out);
 

@@ -42,6 +42,8 @@ struct alignas(64) SegGemmParams {
     int k_half[kMaxSegments];         // dual rank-r segment: A columns [0,k_half) feed the gate half, [k_half,2k_half) the up half
     int dual, epi;
     int group_m, group_n;             // raster (decode_tile)
+    CUtensorMap tmC;                  // BF16 output as 32 x 32 boxes (64 B swizzle) for the epilogue's bulk stores
+    int c_tma;
     void* C2;                         // epi 1: up output; epi 2: d_up output
     void* C3;                         // epi 1: act output
     const __nv_bfloat16* gate_in;     // epi 2: forward gate / up activations
@@ -68,7 +70,7 @@ struct Cfg {
     static constexpr int STAGES = MH == 2 ? 3 : (BN >= 224) ? 4 : (BN == 128) ? 6 : 8;
     static constexpr uint32_t TMEM_COLS = MH == 2 ? 512 : pow2_at_least(2 * BN);
     static constexpr int NCHUNK_B = (BN + 63) / 64;
-    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 16384;   // ring, alignment slack, barriers, epilogue staging
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 32768;   // ring, alignment slack, barriers, epilogue staging
 };
 
 struct TileCoord {
@@ -121,7 +123,7 @@ __device__ __forceinline__ void unpack8_bf16(const uint4& v, float (&f)[8]) {
 // write their row's four 16-byte pieces (XOR-swizzled by row pair: conflict-free both ways), and the warp then moves
 // the tile with 4 lanes per row, 8 rows per instruction - full 32-byte sectors, a quarter of the line operations.
 // Loads of row-distributed inputs (residual, the forward's gate / up) go the same way in reverse.
-constexpr uint32_t kEpiStageBytes = 8 * 2048;   // eight epilogue warps
+constexpr uint32_t kEpiStageBytes = 8 * 2 * 2048;   // eight epilogue warps, two tiles each
 
 __device__ __forceinline__ int stage_slot(int r, int piece) { return r * 4 + (piece ^ ((r >> 1) & 3)); }
 
@@ -159,7 +161,7 @@ __device__ __forceinline__ void stage_load_rows(uint4* stage, int lane, const __
 // -> BF16 / FP32 store (or split-K partial).  `row` is the global output row of this thread's TMEM lane.
 template <int CW>
 __device__ __forceinline__ void epilogue_chunks(const SegGemmParams& p, uint32_t taddr, int row, bool row_ok, int n0,
-                                                int split, int c_lo, int c_hi, uint4* stage) {
+                                                int split, int c_lo, int c_hi, uint4* stage, uint32_t& nchunk) {
     const int lane = threadIdx.x & 31;
 #pragma unroll 1
     for (int c = c_lo; c < c_hi; c++) {
@@ -181,8 +183,16 @@ __device__ __forceinline__ void epilogue_chunks(const SegGemmParams& p, uint32_t
         }
         if constexpr (CW == 32) {
             if (!p.f32) {   // BF16 output: bias / residual / store through the staging tile (whole warp takes part)
+                // two staging tiles per warp alternate, so the bulk store of the previous chunk may still be reading one
+                // while this chunk fills the other; before a tile is reused its store must have finished reading it
+                uint4* st = stage + (nchunk & 1u) * 128;
+                nchunk++;
+                if (p.c_tma) {
+                    if (lane == 0) bulk_wait_read<1>();
+                    __syncwarp();
+                }
                 uint4 res[4];
-                if (p.residual) stage_load_rows(stage, lane, p.residual, p.ldc, row - lane, col0, p.M, p.N, res);
+                if (p.residual) stage_load_rows(st, lane, p.residual, p.ldc, row - lane, col0, p.M, p.N, res);
 #pragma unroll
                 for (int g = 0; g < 4; g++) {
                     const int col = col0 + g * 8;
@@ -201,9 +211,20 @@ __device__ __forceinline__ void epilogue_chunks(const SegGemmParams& p, uint32_t
 #pragma unroll
                         for (int i = 0; i < 8; i++) o[i] += r8[i];
                     }
-                    stage[stage_slot(lane, g)] = pack8_bf16(o);
+                    st[stage_slot(lane, g)] = pack8_bf16(o);
                 }
-                stage_store_tile(stage, lane, reinterpret_cast<__nv_bfloat16*>(p.C), p.ldc, row - lane, col0, p.M, p.N);
+                if (p.c_tma) {
+                    // hand the tile to the TMA engine: the warp goes on to its next chunk while the 2 KB drain to global
+                    // memory in the background (the staging layout IS the 64-byte-swizzled box layout)
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&p.tmC, st, col0, row - lane);
+                        bulk_commit();
+                    }
+                } else {
+                    stage_store_tile(st, lane, reinterpret_cast<__nv_bfloat16*>(p.C), p.ldc, row - lane, col0, p.M, p.N);
+                }
                 continue;
             }
         }
@@ -359,14 +380,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
     using C = Cfg<BN, MH>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    // behind the ring: two 2 KB epilogue staging tiles per epilogue warp (warps 2..9), then the barrier block
+    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 256 : 0);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES + kEpiStageBytes);
     uint64_t* empty = full + C::STAGES;
     uint64_t* tfull = empty + C::STAGES;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // per-warp epilogue staging tile (2 KB each) behind the barrier block; warps 2..9 are the epilogue warps
-    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES + 256) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 128 : 0);
+    uint32_t nchunk = 0;   // chunks this epilogue warp has staged so far (selects one of its two staging tiles)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -535,7 +557,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
                     if (p.epi == 1) { if constexpr (MH == 2 && BN == 256) epilogue_swiglu_fwd(p, taddr, row, tc.n0, 0, 4, stage); continue; }
                     if (p.epi == 2) { epilogue_swiglu_bwd(p, taddr, row, tc.n0, c_lo, c_hi, stage); continue; }
                 }
-                epilogue_chunks<CW>(p, taddr, row, row_ok, tc.n0, tc.split, c_lo, c_hi, stage);
+                epilogue_chunks<CW>(p, taddr, row, row_ok, tc.n0, tc.split, c_lo, c_hi, stage, nchunk);
             }
             tcgen05_fence_before_sync();
             __syncwarp();
@@ -545,6 +567,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
 
 done:
     __syncwarp();
+    if (warp >= 2 && lane == 0) bulk_wait_all();   // this warp's output tiles have reached global memory
     if (*abort_flag) {
         // give copies and MMAs already in flight time to land before shared memory / TMEM go away
         for (int i = 0; i < 200; i++) __nanosleep(1000);
@@ -574,7 +597,7 @@ struct PairCfg {
     static constexpr uint32_t A_BYTES = 256 * BK * 2;
     static constexpr uint32_t B_BYTES = 128 * BK * 2;              // half tile (BN/2 <= 128 rows, or two 64-column chunks)
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 16384;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 32768;
 };
 
 template <int BN>
@@ -584,14 +607,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     constexpr int HALF = BN / 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    // behind the ring: two 2 KB epilogue staging tiles per epilogue warp (warps 2..9), then the barrier block
+    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 256 : 0);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES + kEpiStageBytes);
     uint64_t* empty = full + C::STAGES;
     uint64_t* tfull = empty + C::STAGES;
     uint64_t* tempty = tfull + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // per-warp epilogue staging tile (2 KB each) behind the barrier block; warps 2..9 are the epilogue warps
-    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES + 256) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 128 : 0);
+    uint32_t nchunk = 0;   // chunks this epilogue warp has staged so far (selects one of its two staging tiles)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -702,7 +726,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             tcgen05_fence_after_sync();
             const int row = tc.m0 + int(rank) * 256 + eh * BM + lg * 32 + lane;
             const uint32_t taddr = tmem_base + uint32_t(eh) * 256u + (uint32_t(lg * 32) << 16);
-            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, 0, BN / 32, stage);
+            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, 0, BN / 32, stage, nchunk);
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0);
@@ -711,6 +735,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
 done:
     __syncwarp();
+    if (warp >= 2 && lane == 0) bulk_wait_all();   // this warp's output tiles have reached global memory
     if (*abort_flag) {
         for (int i = 0; i < 200; i++) __nanosleep(1000);
     }
@@ -740,7 +765,7 @@ struct Pair2Cfg {
     static constexpr uint32_t A_BYTES = 128 * BK * 2;
     static constexpr uint32_t B_BYTES = 128 * BK * 2;              // half tile: BN/2 <= 128 rows, or two 64-column chunks
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 16384;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 32768;
 };
 
 template <int BN>
@@ -750,14 +775,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     constexpr int HALF = BN / 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    // behind the ring: two 2 KB epilogue staging tiles per epilogue warp (warps 2..9), then the barrier block
+    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 256 : 0);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES + kEpiStageBytes);
     uint64_t* empty = full + C::STAGES;
     uint64_t* tfull = empty + C::STAGES;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // per-warp epilogue staging tile (2 KB each) behind the barrier block; warps 2..9 are the epilogue warps
-    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES + 256) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 128 : 0);
+    uint32_t nchunk = 0;   // chunks this epilogue warp has staged so far (selects one of its two staging tiles)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -899,7 +925,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             const uint32_t taddr = tmem_base + buf * 256u + (uint32_t(lg * 32) << 16);
             if (p.epi == 1)      epilogue_swiglu_fwd(p, taddr, row, tc.n0, eh * 2, eh * 2 + 2, stage);
             else if (p.epi == 2) epilogue_swiglu_bwd(p, taddr, row, tc.n0, c_lo, c_hi, stage);
-            else                 epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, c_lo, c_hi, stage);
+            else                 epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, c_lo, c_hi, stage, nchunk);
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0 + buf * 8);
@@ -908,6 +934,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
 done:
     __syncwarp();
+    if (warp >= 2 && lane == 0) bulk_wait_all();   // this warp's output tiles have reached global memory
     if (*abort_flag) {
         for (int i = 0; i < 200; i++) __nanosleep(1000);
     }
@@ -1127,6 +1154,12 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     // Column bands and L2 evict_first / evict_last hints on the operand loads were tried and raised traffic.
     p.group_m = ctx->gemm_group_m > 0 ? ctx->gemm_group_m : ((dual ? (N + 127) / 128 : (N + bn - 1) / bn) <= 24 ? 4 : GROUP_M);
     p.group_n = ctx->gemm_group_n;
+    p.c_tma = 0;
+    if (!out.f32 && out.epi == 0 && bn >= 32) {   // BF16 output leaves through bulk tensor stores of 32 x 32 boxes
+        auto tmap_fn = out.no_host_state ? encode_tmap_bf16 : ta::get_tmap_bf16;
+        if (int rc = tmap_fn(ctx, out.C, uint64_t(N), uint64_t(M), uint64_t(out.ldc) * 2, 32, 32, &p.tmC)) return rc;
+        p.c_tma = 1;
+    }
     p.dual = dual; p.epi = out.epi; p.C2 = out.C2; p.C3 = out.C3; p.gate_in = out.gate_in; p.up_in = out.up_in;
 
     const int m_tiles = (M + tile_m - 1) / tile_m, n_tiles = dual ? (N + 127) / 128 : (N + bn - 1) / bn;
