@@ -181,13 +181,13 @@ __global__ void __launch_bounds__(320, 1) attn_fwd_kernel(const __grid_constant_
             uint64_t t0 = 0;
             for (uint32_t spin = 0; jk < n || jv < n; ++spin) {
                 bool progress = false;
-                if (jk < n && mbar_try_wait(&k_empty[jk % KS], ((jk / KS) & 1) ^ 1u)) {
+                if (jk < n && mbar_test_wait(&k_empty[jk % KS], ((jk / KS) & 1) ^ 1u)) {
                     const int kst = jk % KS;
                     mbar_arrive_expect_tx(&k_full[kst], TB);
                     load_tile<HD>(smem + OFF_K + kst * TB, 16384, &p.tmK, &k_full[kst], hk * HD, b * p.T + jk * 128);
                     jk++; progress = true;
                 }
-                if (jv < n && mbar_try_wait(&v_empty[jv & 1], ((jv >> 1) & 1) ^ 1u)) {
+                if (jv < n && mbar_test_wait(&v_empty[jv & 1], ((jv >> 1) & 1) ^ 1u)) {
                     const int st = jv & 1;
                     mbar_arrive_expect_tx(&v_full[st], TB);
                     load_tile<HD>(smem + OFF_V + st * TB, 16384, &p.tmV, &v_full[st], hk * HD, b * p.T + jv * 128);
@@ -211,26 +211,44 @@ __global__ void __launch_bounds__(320, 1) attn_fwd_kernel(const __grid_constant_
             const uint64_t dQd = desc_k(smem_u32(smem + OFF_Q)), dKd = desc_k(smem_u32(smem + OFF_K)),
                            dVd = desc_mn(smem_u32(smem + OFF_V), 16384), dPd = desc_k(smem_u32(smem + OFF_P));
             ATT_WAIT(q_full, 0, DS_TIMEOUT_MMA);
-            // Scores run TWO tiles ahead of the softmax: S(j+2) is issued as soon as the softmax warps have
-            // pulled S(j) into registers, so a finished softmax never waits for its next tile.
-            for (int j = -2; j < n; j++) {
-                if (j + 2 < n) {
-                    const int jn = j + 2, st = jn & 1, kst = jn % KS;
-                    ATT_WAIT(&k_full[kst], (jn / KS) & 1, DS_TIMEOUT_MMA);
-                    ATT_WAIT(&s_empty[st], ((jn >> 1) & 1) ^ 1u, DS_TIMEOUT_MMA);
-                    tcgen05_fence_after_sync();
-                    mma_kk<HD, 128>(tmem + st * 128, dQd, 16384, dKd + ((kst * TB) >> 4), 16384, false);
-                    umma_commit(&k_empty[kst]);
-                    umma_commit(&s_full[st]);
+            // Two cursors, polled: the scores S(js) are issued as soon as their K tile has landed and the softmax
+            // group has pulled S(js-2) into registers; O += P.V of tile jp as soon as its group has published P.
+            // Neither waits behind the other - a P that is still being exponentiated must not hold back the
+            // scores the OTHER group is about to need.
+            int js = 0, jp = 0;
+            uint64_t t0 = 0;
+            for (uint32_t spin = 0; jp < n; ++spin) {
+                bool progress = false;
+                if (js < n) {
+                    const int st = js & 1, kst = js % KS;
+                    if (mbar_test_wait(&k_full[kst], (js / KS) & 1) && mbar_test_wait(&s_empty[st], ((js >> 1) & 1) ^ 1u)) {
+                        tcgen05_fence_after_sync();
+                        mma_kk<HD, 128>(tmem + st * 128, dQd, 16384, dKd + ((kst * TB) >> 4), 16384, false);
+                        umma_commit(&k_empty[kst]);
+                        umma_commit(&s_full[st]);
+                        js++; progress = true;
+                    }
                 }
-                if (j >= 0) {      // O += P_j . V_j once the softmax warps have published P_j (and rescaled O)
-                    const int st = j & 1;
-                    ATT_WAIT(&v_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
-                    ATT_WAIT(&p_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);
-                    tcgen05_fence_after_sync();
-                    mma_kmn<HD, 128>(TM_O + st * HD, dPd + ((st * PB) >> 4), dVd + ((st * TB) >> 4), j > 1);
-                    umma_commit(&v_empty[st]);
-                    umma_commit(&o_full[st]);
+                if (jp < js) {      // O += P_j . V_j once the softmax warps have published P_j (and rescaled O)
+                    const int st = jp & 1;
+                    if (mbar_test_wait(&p_full[st], (jp >> 1) & 1) && mbar_test_wait(&v_full[st], (jp >> 1) & 1)) {
+                        tcgen05_fence_after_sync();
+                        mma_kmn<HD, 128>(TM_O + st * HD, dPd + ((st * PB) >> 4), dVd + ((st * TB) >> 4), jp > 1);
+                        umma_commit(&v_empty[st]);
+                        umma_commit(&o_full[st]);
+                        jp++; progress = true;
+                    }
+                }
+                if (progress) { t0 = 0; continue; }
+                if ((spin & 63u) == 63u) {       // bounded like every other wait of the kernel
+                    if (*abort_flag) goto done;
+                    const uint64_t now = globaltimer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > WAIT_LIMIT_NS) {
+                        *abort_flag = 1;
+                        atomicCAS(p.status, 0, int(DS_TIMEOUT_MMA));
+                        goto done;
+                    }
                 }
             }
         }
@@ -256,16 +274,24 @@ __global__ void __launch_bounds__(320, 1) attn_fwd_kernel(const __grid_constant_
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[grp]);   // the scores are in registers: S buffer is free
-            float mx = -INFINITY;
+            if (diag) {      // the diagonal tile starts at this CTA's first query, so key column > row is the future
 #pragma unroll
-            for (int c = 0; c < 4; c++)
+                for (int c = 0; c < 4; c++)
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float v = __uint_as_float(s[c][i]) * p.scale_log2;
-                    if (diag && (j * 128 + c * 32 + i > q_idx)) v = -INFINITY;
-                    s[c][i] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
-                }
+                    for (int i = 0; i < 32; i++)
+                        if (c * 32 + i > row) s[c][i] = 0xff800000u;   // -inf
+            }
+            // row maximum of the RAW scores (the scale is positive, so it commutes with the maximum): four
+            // independent chains of three-input maxima
+            float mc[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                float a = fmax3(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]), __uint_as_float(s[c][2]));
+#pragma unroll
+                for (int i = 3; i < 31; i += 2) a = fmax3(a, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+                mc[c] = fmaxf(a, __uint_as_float(s[c][31]));
+            }
+            const float mx = fmax3(mc[0], mc[1], fmaxf(mc[2], mc[3])) * p.scale_log2;
             float alpha = 1.f;
             bool rescale = false;
             if (j < 2) {
@@ -275,38 +301,47 @@ __global__ void __launch_bounds__(320, 1) attn_fwd_kernel(const __grid_constant_
                 m = mx;
                 rescale = true;
             }
-            uint32_t pk[64];
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; c++)
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2_approx(__uint_as_float(s[c][i]) - m), p1 = ex2_approx(__uint_as_float(s[c][i + 1]) - m);
-                    sum += p0 + p1;
-                    pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
-                }
             if (j >= 2) {
-                // this group's P buffer and accumulator were last used by P.V of its previous tile (j-2)
+                // this group's P buffer and accumulator were last used by P.V of its previous tile (j-2), issued a
+                // whole tile ago
                 ATT_WAIT(&o_full[grp], ph ^ 1u, DS_TIMEOUT_SOFTMAX);
                 tcgen05_fence_after_sync();
                 if (__any_sync(0xffffffffu, rescale)) {
+                    // rare (the running maximum rose by more than the threshold): eight columns at a time, the scores
+                    // of this tile are still live in registers
 #pragma unroll 1
-                    for (int c = 0; c < HD / 32; c++) {
-                        uint32_t r[32];
-                        tmem_ld_x32(TM_OG + lane_addr + c * 32, r);
+                    for (int c = 0; c < HD / 8; c++) {
+                        uint32_t r[8];
+                        tmem_ld_x8(TM_OG + lane_addr + c * 8, r);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st_x32(TM_OG + lane_addr + c * 32, r);
+                        for (int i = 0; i < 8; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st_x8(TM_OG + lane_addr + c * 8, r);
                     }
                     tmem_st_wait();
                 }
             }
-            l = l * alpha + sum;
+            // p = 2^(s*scale - m): the scale rides in the fused multiply-add, two elements per instruction; every
+            // eight probabilities leave for the P tile at once
+            const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nm2 = pack_f32x2(-m, -m);
+            uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-            for (int g = 0; g < 16; g++)
-                *reinterpret_cast<uint4*>(sP + kmajor_off(row, g * 8)) =
-                    make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int i = g * 8 + e * 2;
+                        const float2 x = unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nm2));
+                        const float p0 = ex2_approx(x.x), p1 = ex2_approx(x.y);
+                        sum2[e & 1] = fadd2(sum2[e & 1], pack_f32x2(p0, p1));
+                        w[e] = pack_bf16x2(p0, p1);
+                    }
+                    *reinterpret_cast<uint4*>(sP + kmajor_off(row, c * 32 + g * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            const float2 sum_lh = unpack_f32x2(fadd2(sum2[0], sum2[1]));
+            l = l * alpha + (sum_lh.x + sum_lh.y);
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
             __syncwarp();
@@ -500,6 +535,8 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_consta
         const size_t stat = (size_t(b) * p.Hq + h) * p.T + q_idx;
         const float lse2 = ok ? p.lse[stat] * kLog2e : INFINITY;
         const float dlt = ok ? p.delta[stat] : 0.f;
+        const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse2, -lse2);
+        const uint64_t scale2 = pack_f32x2(p.scale, p.scale), nd2 = pack_f32x2(-dlt * p.scale, -dlt * p.scale);
         for (int j = grp; j < n; j += 2) {
             const int st = grp;
             const uint32_t ph = (j >> 1) & 1;
@@ -512,28 +549,25 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_consta
                 tmem_ld_x32(TM_DP + st * 64 + lane_addr + c * 32, rp[c]);
             }
             tmem_ld_wait();
-            const bool diag = (j * 64 + 63 > q0);
-            // staged so that the 64 special-function ops issue back to back (see the forward kernel)
+            if (j * 64 + 63 > q0) {      // sub-tile on the diagonal: keys after this row's query are the future
 #pragma unroll
-            for (int c = 0; c < 2; c++)
+                for (int c = 0; c < 2; c++)
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float a = __uint_as_float(rs[c][i]) * p.scale_log2 - lse2;
-                    if (diag && (j * 64 + c * 32 + i > q_idx)) a = -INFINITY;
-                    rs[c][i] = __float_as_uint(a);
-                }
-#pragma unroll
-            for (int c = 0; c < 2; c++)
-#pragma unroll
-                for (int i = 0; i < 32; i++) rs[c][i] = __float_as_uint(ex2_approx(__uint_as_float(rs[c][i])));
+                    for (int i = 0; i < 32; i++)
+                        if (j * 64 + c * 32 + i > q_idx) rs[c][i] = 0xff800000u;   // -inf -> probability 0
+            }
+            // p = 2^(s*scale*log2e - lse*log2e), dS = p * (dP - delta) * scale: two elements per instruction
             uint32_t pk[32];
 #pragma unroll
             for (int c = 0; c < 2; c++)
 #pragma unroll
-                for (int i = 0; i < 32; i += 2)
-                    pk[c * 16 + (i >> 1)] =
-                        pack_bf16x2(__uint_as_float(rs[c][i]) * (__uint_as_float(rp[c][i]) - dlt) * p.scale,
-                                    __uint_as_float(rs[c][i + 1]) * (__uint_as_float(rp[c][i + 1]) - dlt) * p.scale);
+                for (int i = 0; i < 32; i += 2) {
+                    const float2 a = unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(rs[c][i]), __uint_as_float(rs[c][i + 1])), sc2, nl2));
+                    const uint64_t pp = pack_f32x2(ex2_approx(a.x), ex2_approx(a.y));
+                    const uint64_t t = ffma2(pack_f32x2(__uint_as_float(rp[c][i]), __uint_as_float(rp[c][i + 1])), scale2, nd2);
+                    const float2 ds = unpack_f32x2(fmul2(pp, t));
+                    pk[c * 16 + (i >> 1)] = pack_bf16x2(ds.x, ds.y);
+                }
             tmem_st_x32(TM_DP + st * 64 + lane_addr, pk);   // dS back into this thread's dP row (first 32 columns)
             tmem_st_wait();
             tcgen05_fence_before_sync();
@@ -580,7 +614,8 @@ template <int HD>
 __global__ void __launch_bounds__(320, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
     constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
     constexpr int QST = kDkvStages;   // Q/dO ring depth (a stage is released only after dV, dK consumed it)
-    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + QST * TB64, OFF_BAR = 2 * TB + 2 * QST * TB64;
+    constexpr uint32_t OFF_K = 0, OFF_V = TB, OFF_Q = 2 * TB, OFF_DO = 2 * TB + QST * TB64, OFF_BAR = 2 * TB + 2 * QST * TB64,
+                       OFF_STAT = OFF_BAR + 256;   // 8 warps x 128 floats of per-query statistics
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
@@ -686,6 +721,8 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dkv_kernel(const __grid_const
         };
         float next_l[2], next_d[2];
         fetch(grp, next_l, next_d);
+        float* stat = reinterpret_cast<float*>(smem + OFF_STAT) + (warp - 2) * 128;
+        const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), scale2 = pack_f32x2(p.scale, p.scale);
         for (int it = grp; it < iters; it += 2) {
             const int qs = 2 * kt + it % per_head, st = grp;
             const uint32_t ph = (it >> 1) & 1;
@@ -700,22 +737,38 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dkv_kernel(const __grid_const
                 tmem_ld_x32(TM_DPT + st * 64 + lane_addr + c * 32, rp[c]);
             }
             tmem_ld_wait();
-            const bool diag = (qs * 64 < kv0 + 127);
+            if (qs * 64 < kv0 + 127) {   // sub-tile on the diagonal: queries before this row's key cannot see it
+                const int first = kv_idx - qs * 64;      // columns below this are masked
+#pragma unroll
+                for (int c = 0; c < 2; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (c * 32 + i < first) rs[c][i] = 0xff800000u;   // -inf -> probability 0
+            }
+            // the sub-tile's 64 (-lse*log2e) and 64 (-delta*scale) go through this warp's own slot of shared memory
+            // and come back as broadcast 16-byte loads: four columns per load, already paired for the packed math
+            stat[lane] = -cl[0]; stat[32 + lane] = -cl[1];
+            stat[64 + lane] = -cd[0] * p.scale; stat[96 + lane] = -cd[1] * p.scale;
+            __syncwarp();
             uint32_t pk[32], dk[32];
 #pragma unroll
             for (int c = 0; c < 2; c++)
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int col = c * 32 + i;
-                    float a0 = __uint_as_float(rs[c][i]) * p.scale_log2 - __shfl_sync(0xffffffffu, cl[c], i);
-                    float a1 = __uint_as_float(rs[c][i + 1]) * p.scale_log2 - __shfl_sync(0xffffffffu, cl[c], i + 1);
-                    if (diag && (kv_idx > qs * 64 + col)) a0 = -INFINITY;
-                    if (diag && (kv_idx > qs * 64 + col + 1)) a1 = -INFINITY;
-                    const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
-                    pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
-                    dk[c * 16 + (i >> 1)] =
-                        pack_bf16x2(p0 * (__uint_as_float(rp[c][i]) - __shfl_sync(0xffffffffu, cd[c], i)) * p.scale,
-                                    p1 * (__uint_as_float(rp[c][i + 1]) - __shfl_sync(0xffffffffu, cd[c], i + 1)) * p.scale);
+                for (int i = 0; i < 32; i += 4) {
+                    const ulonglong2 nl = *reinterpret_cast<const ulonglong2*>(stat + c * 32 + i);
+                    const ulonglong2 nd = *reinterpret_cast<const ulonglong2*>(stat + 64 + c * 32 + i);
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {
+                        const int e = i + hh * 2;
+                        const float2 a = unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(rs[c][e]), __uint_as_float(rs[c][e + 1])), sc2,
+                                                            hh ? nl.y : nl.x));
+                        const float p0 = ex2_approx(a.x), p1 = ex2_approx(a.y);
+                        pk[c * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
+                        const uint64_t t = ffma2(pack_f32x2(__uint_as_float(rp[c][e]), __uint_as_float(rp[c][e + 1])), scale2,
+                                                 hh ? nd.y : nd.x);
+                        const float2 ds = unpack_f32x2(fmul2(pack_f32x2(p0, p1), t));
+                        dk[c * 16 + (e >> 1)] = pack_bf16x2(ds.x, ds.y);
+                    }
                 }
             // P^T and dS^T go back into this thread's own rows of the S^T / dP^T buffers (first 32 columns)
             tmem_st_x32(TM_ST + st * 64 + lane_addr, pk);
@@ -760,7 +813,7 @@ done:
 
 template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 2 * 32768 + 256 + 1024; }
 template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 2 * kDqStages * Tile<HD>::BYTES64 + 256 + 1024; }
-template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 256 + 1024; }
+template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 256 + 8 * 512 + 1024; }
 
 int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const void* V, const void* dO, int B, int T,
               int Hq, int Hkv, int hd) {
