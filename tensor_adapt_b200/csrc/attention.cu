@@ -7,7 +7,7 @@
 //
 //   attn_fwd_kernel     CTA = (128 query rows, head, batch); S = Q.K^T and O_j = P.V per 128-key tile
 //   attn_delta_kernel   delta[b,h,t] = sum_d dO*O
-//   attn_bwd_dq_kernel  CTA = (128 query rows, head, batch); dQ accumulates in TMEM over key tiles
+//   attn_bwd_dq_kernel  CTA = (128 query rows, head, batch); dQ accumulates in TMEM over 128-key tiles
 //   attn_bwd_dkv_kernel CTA = (128 key rows, KV head, batch); dK, dV accumulate in TMEM over all query
 //                       tiles AND all query heads of the GQA group, so no atomics are needed
 //
@@ -29,7 +29,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 struct AttnParams {
     CUtensorMap tmQ, tmK, tmV, tmdO;          // boxes of 128 rows
-    CUtensorMap tmQ64, tmK64, tmV64, tmdO64;  // boxes of 64 rows (backward sub-tiles)
+    CUtensorMap tmQ64, tmdO64;                // boxes of 64 rows (query sub-tiles of the dK/dV kernel)
     __nv_bfloat16* out;        // fwd: O ; dq: dQ
     __nv_bfloat16* out2;       // dkv: dK
     __nv_bfloat16* out3;       // dkv: dV
@@ -111,7 +111,6 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, uint32_t chunk_bytes, co
 // A running maximum is only raised when the new one exceeds it by more than this (log2 units): the
 // probabilities then stay below 2^8 and the accumulator in TMEM rarely needs rescaling.
 constexpr float kRescaleThreshold = 8.f;
-constexpr int kDqStages = 4;    // K/V ring of the dQ kernel (64-row tiles)
 constexpr int kDkvStages = 4;   // Q/dO ring of the dK/dV kernel (64-row tiles)
 
 // ─────────────────────────────── forward ───────────────────────────────
@@ -434,25 +433,27 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __
 }
 
 // ─────────────────────────────── backward: dQ ───────────────────────────────
-// CTA = 128 query rows of one head; keys are walked in sub-tiles of 64 so that S and dP can be double
-// buffered in TMEM: S[2] at columns [0,128), dP[2] at [128,256), dQ accumulator at [256, 256+HD).
-// dS never touches shared memory: each element-wise thread overwrites the first 32 columns of its dP row
-// with the BF16 pairs and dQ += dS.K reads that A operand from TMEM (the tensor pipe executes in issue
-// order, so the scores of sub-tile j+2, issued after dQ of sub-tile j, cannot overwrite a dS still in use).
+// CTA = 128 query rows of one head; keys are walked in tiles of 128, so every contraction is an N = 128 MMA (an
+// N = 64 MMA re-reads the 128-row A operand for half the work and runs at shared-memory speed, ~60 clocks for
+// 32).  TMEM: S[2] at columns [0,256) double buffered, dP at [256,384) single, dQ accumulator at [384, 384+HD).
+// The eight element-wise warps work on ONE tile at a time, each group of four on its 64 of the 128 key columns:
+//   S(j), dP(j) complete -> all warps pull their columns into registers (`loaded`) -> the MMA issuer may overwrite
+//   dP with dP(j+1) -> dS = P*(dP-delta)*scale goes back, BF16 pairs, over the first 64 columns of S(j)'s buffer
+//   (`ds_full`) -> dQ += dS(j).K(j) reads that A operand from tensor memory -> S(j+2) reuses the buffer (the
+//   tensor pipe executes in issue order, so it cannot overwrite a dS still being read).
+// While the warps work on tile j the pipe runs dP(j+1); while they work on tile j+1 it runs dQ(j) and S(j+2).
 
 template <int HD>
 __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
-    constexpr uint32_t TB = Tile<HD>::BYTES, TB64 = Tile<HD>::BYTES64;
-    constexpr int KVST = kDqStages;   // K/V ring depth: a stage is only released after dQ += dS.K, so the
-                                      // prefetch distance must cover the TMA latency
-    constexpr uint32_t OFF_Q = 0, OFF_DO = TB, OFF_K = 2 * TB, OFF_V = 2 * TB + KVST * TB64,
-                       OFF_BAR = 2 * TB + 2 * KVST * TB64;
+    constexpr uint32_t TB = Tile<HD>::BYTES;
+    constexpr int KST = 3, VST = 2;   // K is held until dQ += dS.K of its tile has run, V only until dP has
+    constexpr uint32_t OFF_Q = 0, OFF_DO = TB, OFF_K = 2 * TB, OFF_V = (2 + KST) * TB, OFF_BAR = (2 + KST + VST) * TB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-    uint64_t *qdo_full = bars, *kv_full = bars + 1, *kv_empty = bars + 1 + KVST, *s_full = bars + 1 + 2 * KVST,
-             *ds_full = s_full + 2, *dq_full = s_full + 4;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
+    uint64_t *qdo_full = bars, *k_full = bars + 1, *k_empty = bars + 4, *v_full = bars + 7, *v_empty = bars + 9,
+             *s_full = bars + 11, *dp_full = bars + 13, *loaded = bars + 14, *ds_full = bars + 15, *dq_full = bars + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (blockDim.x != 320) {   // the warp roles below assume ten warps: refuse any other launch shape
@@ -464,16 +465,15 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_consta
     const int qt = nt - 1 - int(blockIdx.x) / hb;   // heavy-first over the whole launch
     const int h = (int(blockIdx.x) % hb) % p.Hq, b = (int(blockIdx.x) % hb) / p.Hq;
     const int hk = h / (p.Hq / p.Hkv);
-    const int n = 2 * (qt + 1);    // key sub-tiles of 64 rows: 0 .. 2*qt+1
+    const int n = qt + 1;          // key tiles 0 .. qt
     const int q0 = qt * 128;
 
     if (threadIdx.x == 0) {
         mbar_init(qdo_full, 1);
-        for (int i = 0; i < KVST; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-        for (int i = 0; i < 2; i++) {
-            mbar_init(&s_full[i], 1); mbar_init(&ds_full[i], 4);
-        }
-        mbar_init(dq_full, 1);
+        for (int i = 0; i < KST; i++) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+        for (int i = 0; i < VST; i++) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
+        for (int i = 0; i < 2; i++) mbar_init(&s_full[i], 1);
+        mbar_init(dp_full, 1); mbar_init(loaded, 8); mbar_init(ds_full, 8); mbar_init(dq_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -482,52 +482,83 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_consta
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t TM_S = tmem, TM_DP = tmem + 128, TM_DQ = tmem + 256;
+    const uint32_t TM_S = tmem, TM_DP = tmem + 256, TM_DQ = tmem + 384;
 
     if (warp == 0) {
         if (lane == 0) {
             mbar_arrive_expect_tx(qdo_full, 2 * TB);
             load_tile<HD>(smem + OFF_Q, 16384, &p.tmQ, qdo_full, h * HD, b * p.T + q0);
             load_tile<HD>(smem + OFF_DO, 16384, &p.tmdO, qdo_full, h * HD, b * p.T + q0);
-            for (int j = 0; j < n; j++) {
-                const int st = j % KVST;
-                ATT_WAIT(&kv_empty[st], ((j / KVST) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
-                mbar_arrive_expect_tx(&kv_full[st], 2 * TB64);
-                load_tile<HD>(smem + OFF_K + st * TB64, 8192, &p.tmK64, &kv_full[st], hk * HD, b * p.T + j * 64);
-                load_tile<HD>(smem + OFF_V + st * TB64, 8192, &p.tmV64, &kv_full[st], hk * HD, b * p.T + j * 64);
+            // K and V rings are filled by two independent cursors (their slots free at different times)
+            int jk = 0, jv = 0;
+            uint64_t t0 = 0;
+            for (uint32_t spin = 0; jk < n || jv < n; ++spin) {
+                bool progress = false;
+                if (jk < n && mbar_test_wait(&k_empty[jk % KST], ((jk / KST) & 1) ^ 1u)) {
+                    const int st = jk % KST;
+                    mbar_arrive_expect_tx(&k_full[st], TB);
+                    load_tile<HD>(smem + OFF_K + st * TB, 16384, &p.tmK, &k_full[st], hk * HD, b * p.T + jk * 128);
+                    jk++; progress = true;
+                }
+                if (jv < n && mbar_test_wait(&v_empty[jv % VST], ((jv / VST) & 1) ^ 1u)) {
+                    const int st = jv % VST;
+                    mbar_arrive_expect_tx(&v_full[st], TB);
+                    load_tile<HD>(smem + OFF_V + st * TB, 16384, &p.tmV, &v_full[st], hk * HD, b * p.T + jv * 128);
+                    jv++; progress = true;
+                }
+                if (progress) { t0 = 0; continue; }
+                if ((spin & 63u) == 63u) {       // bounded like every other wait of the kernel
+                    if (*abort_flag) goto done;
+                    const uint64_t now = globaltimer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > WAIT_LIMIT_NS) {
+                        *abort_flag = 1;
+                        atomicCAS(p.status, 0, int(DS_TIMEOUT_PRODUCER));
+                        goto done;
+                    }
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint64_t dQd = desc_k(smem_u32(smem + OFF_Q)), dDOd = desc_k(smem_u32(smem + OFF_DO)),
                            dKk = desc_k(smem_u32(smem + OFF_K)), dVk = desc_k(smem_u32(smem + OFF_V)),
-                           dKmn = desc_mn(smem_u32(smem + OFF_K), 8192);
+                           dKmn = desc_mn(smem_u32(smem + OFF_K), 16384);
             ATT_WAIT(qdo_full, 0, DS_TIMEOUT_MMA);
-            auto scores = [&](int jn) -> bool {      // S = Q . K^T and dP = dO . V^T of key sub-tile jn
-                const int st = jn & 1, ks = jn % KVST;
-                if (!mbar_wait(&kv_full[ks], (jn / KVST) & 1, abort_flag, p.status, DS_TIMEOUT_MMA)) return false;
+            auto scores = [&](int jn) -> bool {      // S = Q . K^T of key tile jn into buffer jn & 1
+                const int ks = jn % KST;
+                if (!mbar_wait(&k_full[ks], (jn / KST) & 1, abort_flag, p.status, DS_TIMEOUT_MMA)) return false;
                 tcgen05_fence_after_sync();
-                mma_kk<HD, 64>(TM_S + st * 64, dQd, 16384, dKk + ((ks * TB64) >> 4), 8192, false);
-                mma_kk<HD, 64>(TM_DP + st * 64, dDOd, 16384, dVk + ((ks * TB64) >> 4), 8192, false);
-                umma_commit(&s_full[st]);
+                mma_kk<HD, 128>(TM_S + (jn & 1) * 128, dQd, 16384, dKk + ((ks * TB) >> 4), 16384, false);
+                umma_commit(&s_full[jn & 1]);
                 return true;
             };
-            for (int jn = 0; jn < 2 && jn < n; jn++)
-                if (!scores(jn)) goto done;
-            for (int j = 0; j < n; j++) {
-                const int st = j & 1, ks = j % KVST;
-                ATT_WAIT(&ds_full[st], (j >> 1) & 1, DS_TIMEOUT_MMA);   // dS of sub-tile j is in TMEM
+            auto dprobs = [&](int jn) -> bool {      // dP = dO . V^T of key tile jn
+                const int vs = jn % VST;
+                if (!mbar_wait(&v_full[vs], (jn / VST) & 1, abort_flag, p.status, DS_TIMEOUT_MMA)) return false;
                 tcgen05_fence_after_sync();
-                mma_tmn<HD, 64>(TM_DQ, TM_DP + st * 64, dKmn + ((ks * TB64) >> 4), j > 0);   // dQ += dS . K
-                umma_commit(&kv_empty[ks]);
-                if (j + 2 < n && !scores(j + 2)) goto done;            // reuses the S / dP buffers just read
+                mma_kk<HD, 128>(TM_DP, dDOd, 16384, dVk + ((vs * TB) >> 4), 16384, false);
+                umma_commit(&v_empty[vs]);
+                umma_commit(dp_full);
+                return true;
+            };
+            if (!scores(0) || !dprobs(0)) goto done;
+            if (n > 1 && !scores(1)) goto done;
+            for (int j = 0; j < n; j++) {
+                if (j + 1 < n) {
+                    ATT_WAIT(loaded, j & 1, DS_TIMEOUT_MMA);      // dP(j) is in registers: its buffer is free
+                    if (!dprobs(j + 1)) goto done;
+                }
+                ATT_WAIT(ds_full, j & 1, DS_TIMEOUT_MMA);         // dS of tile j is in TMEM
+                tcgen05_fence_after_sync();
+                mma_tmn<HD, 128>(TM_DQ, TM_S + (j & 1) * 128, dKmn + (((j % KST) * TB) >> 4), j > 0);   // dQ += dS . K
+                umma_commit(&k_empty[j % KST]);
+                if (j + 2 < n && !scores(j + 2)) goto done;       // reuses the buffer dS(j) was just read from
             }
             umma_commit(dq_full);
         }
     } else {
-        // Two groups of four element-wise warps: group g owns the key sub-tiles of parity g with the S / dP
-        // buffers of that parity; dQ is a plain sum, so both groups feed the same accumulator.
-        const int lg = warp & 3, grp = (warp - 2) >> 2;
+        const int lg = warp & 3, grp = (warp - 2) >> 2;   // grp: which 64 of the tile's 128 key columns
         const int row = lg * 32 + lane;
         const int q_idx = q0 + row;
         const bool ok = q_idx < p.T;
@@ -537,24 +568,27 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_consta
         const float dlt = ok ? p.delta[stat] : 0.f;
         const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse2, -lse2);
         const uint64_t scale2 = pack_f32x2(p.scale, p.scale), nd2 = pack_f32x2(-dlt * p.scale, -dlt * p.scale);
-        for (int j = grp; j < n; j += 2) {
-            const int st = grp;
-            const uint32_t ph = (j >> 1) & 1;
-            ATT_WAIT(&s_full[st], ph, DS_TIMEOUT_SOFTMAX);
+        for (int j = 0; j < n; j++) {
+            const uint32_t tS = TM_S + (j & 1) * 128 + lane_addr;
+            ATT_WAIT(&s_full[j & 1], (j >> 1) & 1, DS_TIMEOUT_SOFTMAX);
+            ATT_WAIT(dp_full, j & 1, DS_TIMEOUT_SOFTMAX);
             tcgen05_fence_after_sync();
             uint32_t rs[2][32], rp[2][32];
 #pragma unroll
             for (int c = 0; c < 2; c++) {
-                tmem_ld_x32(TM_S + st * 64 + lane_addr + c * 32, rs[c]);
-                tmem_ld_x32(TM_DP + st * 64 + lane_addr + c * 32, rp[c]);
+                tmem_ld_x32(tS + grp * 64 + c * 32, rs[c]);
+                tmem_ld_x32(TM_DP + lane_addr + grp * 64 + c * 32, rp[c]);
             }
             tmem_ld_wait();
-            if (j * 64 + 63 > q0) {      // sub-tile on the diagonal: keys after this row's query are the future
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(loaded);
+            if (j == qt) {      // the diagonal tile starts at this CTA's first query: key column > row is the future
 #pragma unroll
                 for (int c = 0; c < 2; c++)
 #pragma unroll
                     for (int i = 0; i < 32; i++)
-                        if (j * 64 + c * 32 + i > q_idx) rs[c][i] = 0xff800000u;   // -inf -> probability 0
+                        if (grp * 64 + c * 32 + i > row) rs[c][i] = 0xff800000u;   // -inf -> probability 0
             }
             // p = 2^(s*scale*log2e - lse*log2e), dS = p * (dP - delta) * scale: two elements per instruction
             uint32_t pk[32];
@@ -568,11 +602,15 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_consta
                     const float2 ds = unpack_f32x2(fmul2(pp, t));
                     pk[c * 16 + (i >> 1)] = pack_bf16x2(ds.x, ds.y);
                 }
-            tmem_st_x32(TM_DP + st * 64 + lane_addr, pk);   // dS back into this thread's dP row (first 32 columns)
+            // dS goes over columns [32 grp, 32 grp + 32) of the score buffer; those hold scores of the OTHER group's
+            // half when grp == 1, so every warp must have pulled its scores first
+            ATT_WAIT(loaded, j & 1, DS_TIMEOUT_SOFTMAX);
+            tcgen05_fence_after_sync();
+            tmem_st_x32(tS + grp * 32, pk);
             tmem_st_wait();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&ds_full[st]);
+            if (lane == 0) mbar_arrive(ds_full);
         }
         ATT_WAIT(dq_full, 0, DS_TIMEOUT_SOFTMAX);
         tcgen05_fence_after_sync();
@@ -812,7 +850,7 @@ done:
 }
 
 template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 2 * 32768 + 256 + 1024; }
-template <int HD> constexpr size_t dq_smem()  { return 2 * Tile<HD>::BYTES + 2 * kDqStages * Tile<HD>::BYTES64 + 256 + 1024; }
+template <int HD> constexpr size_t dq_smem()  { return 7 * Tile<HD>::BYTES + 256 + 1024; }
 template <int HD> constexpr size_t dkv_smem() { return 2 * Tile<HD>::BYTES + 2 * kDkvStages * Tile<HD>::BYTES64 + 256 + 8 * 512 + 1024; }
 
 int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const void* V, const void* dO, int B, int T,
@@ -826,8 +864,6 @@ int make_maps(ta_ctx* ctx, AttnParams& p, const void* Q, const void* K, const vo
         if ((rc = get_tmap_bf16(ctx, dO, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 128, &p.tmdO))) return rc;
         if ((rc = get_tmap_bf16(ctx, dO, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 64, &p.tmdO64))) return rc;
         if ((rc = get_tmap_bf16(ctx, Q, uint64_t(Hq) * hd, rows, uint64_t(Hq) * hd * 2, 64, 64, &p.tmQ64))) return rc;
-        if ((rc = get_tmap_bf16(ctx, K, uint64_t(Hkv) * hd, rows, uint64_t(Hkv) * hd * 2, 64, 64, &p.tmK64))) return rc;
-        if ((rc = get_tmap_bf16(ctx, V, uint64_t(Hkv) * hd, rows, uint64_t(Hkv) * hd * 2, 64, 64, &p.tmV64))) return rc;
     }
     return TA_OK;
 }
