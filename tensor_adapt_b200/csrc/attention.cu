@@ -30,6 +30,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 struct AttnParams {
     CUtensorMap tmQ, tmK, tmV, tmdO;          // boxes of 128 rows
     CUtensorMap tmQ64, tmdO64;                // boxes of 64 rows (query sub-tiles of the dK/dV kernel)
+    CUtensorMap tmOut;                        // fwd: O, dq: dQ; box of 32 rows x 64 columns (one warp's share of a tile)
     __nv_bfloat16* out;        // fwd: O ; dq: dQ
     __nv_bfloat16* out2;       // dkv: dK
     __nv_bfloat16* out3;       // dkv: dV
@@ -103,6 +104,23 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, uint32_t chunk_bytes, co
                                           int col0, int row0) {
 #pragma unroll
     for (int c = 0; c < Tile<HD>::NC; c++) tma_load_2d(dst + c * chunk_bytes, tm, bar, col0 + 64 * c, row0);
+}
+
+// Output tiles leave through a 4 KB staging tile per warp (32 rows x 128 B in the 128-byte-swizzled layout of a
+// {64, 32} TMA box) and ONE bulk tensor store, instead of 8 x 32 scattered 16-byte stores per thread row.
+// Only for tiles that lie wholly inside their sequence: a bulk store clips at the end of the tensor, not of the batch.
+__device__ __forceinline__ void stage_row_chunk(uint8_t* st, int lane, int j, uint4 v) {
+    *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+}
+__device__ __forceinline__ void stage_flush(const CUtensorMap* tm, uint8_t* st, int lane, int col0, int row0) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(tm, st, col0, row0);
+        bulk_commit();
+        bulk_wait_read<0>();     // the tile has been read: shared memory may go away with the CTA
+    }
+    __syncwarp();
 }
 
 #define ATT_WAIT(bar, parity, code) \
@@ -370,6 +388,8 @@ __global__ void __launch_bounds__(320, 1) attn_fwd_kernel(const __grid_constant_
         const bool ok = q_idx < p.T;
         __nv_bfloat16* orow = p.out + (size_t(b) * p.T + q_idx) * (size_t(p.Hq) * HD) + h * HD;
         // each group normalises and stores half of the head dimension
+        const bool bulk = HD == 128 && q0 + 128 <= p.T;
+        uint8_t* st = sP + 4096 + lg * 4096;     // past the (max, sum) exchange area of this group's idle P buffer
 #pragma unroll
         for (int c = grp * (HD / 64); c < (grp + 1) * (HD / 64); c++) {
             uint32_t r0[32], r1[32];
@@ -387,10 +407,12 @@ __global__ void __launch_bounds__(320, 1) attn_fwd_kernel(const __grid_constant_
                         if (both) { a0 += __uint_as_float(r1[e]) * f1; a1 += __uint_as_float(r1[e + 1]) * f1; }
                         w[i] = pack_bf16x2(a0, a1);
                     }
-                    *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (bulk) stage_row_chunk(st, lane, (c - grp * (HD / 64)) * 4 + g, make_uint4(w[0], w[1], w[2], w[3]));
+                    else *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
         }
+        if (bulk) stage_flush(&p.tmOut, st, lane, h * HD + grp * 64, b * p.T + q0 + lg * 32);
         if (ok && grp == 0) p.lse[(size_t(b) * p.Hq + h) * p.T + q_idx] = M * kLn2 + logf(L);
     }
 done:
@@ -615,6 +637,8 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_consta
         ATT_WAIT(dq_full, 0, DS_TIMEOUT_SOFTMAX);
         tcgen05_fence_after_sync();
         __nv_bfloat16* orow = p.out + (size_t(b) * p.T + q_idx) * (size_t(p.Hq) * HD) + h * HD;
+        const bool bulk = HD == 128 && q0 + 128 <= p.T;
+        uint8_t* st = smem + OFF_K + (warp - 2) * 4096;     // the K ring is idle once dq_full has fired
 #pragma unroll
         for (int c = grp * (HD / 64); c < (grp + 1) * (HD / 64); c++) {   // each group stores half of the head dimension
             uint32_t r[32];
@@ -627,10 +651,12 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dq_kernel(const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 4; i++)
                         w[i] = pack_bf16x2(__uint_as_float(r[g * 8 + i * 2]), __uint_as_float(r[g * 8 + i * 2 + 1]));
-                    *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (bulk) stage_row_chunk(st, lane, (c - grp * (HD / 64)) * 4 + g, make_uint4(w[0], w[1], w[2], w[3]));
+                    else *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
         }
+        if (bulk) stage_flush(&p.tmOut, st, lane, h * HD + grp * 64, b * p.T + q0 + lg * 32);
     }
 done:
     __syncwarp();
@@ -895,6 +921,7 @@ int ta_flash_attn_fwd(ta_ctx* ctx, const void* Q, const void* K, const void* V, 
     AttnParams p{};
     if (int rc = make_maps(ctx, p, Q, K, V, nullptr, B, T, Hq, Hkv, head_dim)) return rc;
     p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse;
+    if (int rc = get_tmap_bf16(ctx, out, uint64_t(Hq) * head_dim, uint64_t(B) * T, uint64_t(Hq) * head_dim * 2, 64, 32, &p.tmOut)) return rc;
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
     p.scale = 1.f / std::sqrt(float(head_dim)); p.scale_log2 = p.scale * kLog2e; p.status = ctx->d_status;
     const dim3 grid(((T + 127) / 128) * Hq * B);
@@ -935,6 +962,7 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
     p.scale = 1.f / std::sqrt(float(head_dim)); p.scale_log2 = p.scale * kLog2e; p.status = ctx->d_status;
     p.out = static_cast<__nv_bfloat16*>(dQ);
+    if (int rc = get_tmap_bf16(ctx, dQ, uint64_t(Hq) * head_dim, uint64_t(B) * T, uint64_t(Hq) * head_dim * 2, 64, 32, &p.tmOut)) return rc;
     p.out2 = static_cast<__nv_bfloat16*>(dK);
     p.out3 = static_cast<__nv_bfloat16*>(dV);
     const int nt = (T + 127) / 128;
