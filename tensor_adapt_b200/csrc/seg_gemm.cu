@@ -865,7 +865,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             const uint32_t peer_empty0 = map_to_cta(smem_u32(&empty[0]), 1), peer_tfull0 = map_to_cta(smem_u32(&tfull[0]), 1);
-            uint32_t it = 0, lt = 0;
+            // One MMA covers 128 clocks of tensor work for the pair, so the issuing thread has ~128 clocks per MMA for
+            // everything else: descriptors are built once (stage 0) and advanced with one 64-bit add (the start-address
+            // field counts 16-byte units and never carries: shared-memory addresses stay below 256 KB).
+            const uint32_t s0 = smem_u32(smem);
+            const uint64_t a_d0 = smem_desc_sw128(s0, 16, 1024);
+            const uint64_t bk_d0 = smem_desc_sw128(s0 + C::A_BYTES, 16, 1024), bmn_d0 = smem_desc_sw128(s0 + C::A_BYTES, 8192, 1024);
+            const uint32_t empty0 = smem_u32(&empty[0]);
+            uint32_t it = 0, lt = 0, stage = 0, ph = 0;
             for (int tile = pair; tile < total; tile += npairs, lt++) {
                 const uint32_t buf = lt & 1u, use = lt >> 1;
                 if (!mbar_wait(&tempty[buf], (use & 1u) ^ 1u, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
@@ -876,32 +883,40 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     const int nkb = (p.K[s] + BK - 1) / BK;
                     const bool b_mn = p.b_mn[s] != 0;
                     const uint32_t idesc = umma_idesc_bf16(256, BN, false, b_mn);
+                    const uint64_t b_d0 = b_mn ? bmn_d0 : bk_d0;
+                    const uint64_t b_step = b_mn ? (2048u >> 4) : (32u >> 4);
+                    const bool dual_r = p.dual && p.k_half[s];
                     for (int kb = 0; kb < nkb; kb++, it++) {
-                        const uint32_t stage = it % C::STAGES;
-                        const uint32_t ph = (it / C::STAGES) & 1u;
                         if (!mbar_wait(&full[stage], ph, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
                         tcgen05_fence_after_sync();
-                        const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
-                        const uint32_t sb = sa + C::A_BYTES;
+                        const uint64_t so = uint64_t(stage * C::STAGE_BYTES) >> 4;
                         const int krem = p.K[s] - kb * BK;
-                        const int kinstr = krem >= BK ? 4 : (krem + 15) / 16;
-                        if (p.dual && p.k_half[s]) {
+                        if (dual_r) {
+                            const uint32_t sa = s0 + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+                            const int kinstr = krem >= BK ? 4 : (krem + 15) / 16;
                             const uint32_t idesc_h = umma_idesc_bf16(256, 128, false, false);
                             for (int ki = 0; ki < kinstr; ki++) {
                                 const DualStep ds = dual_step(kb * BK + ki * 16, p.k_half[s], kb);
                                 umma_bf16_pair(d_tmem + ds.half * 128, smem_desc_sw128(sa + ki * 32, 16, 1024),
                                                smem_desc_sw128(sb + ds.half * 8192 + ds.b_off, 16, 1024), idesc_h, acc);
                             }
+                        } else if (krem >= BK) {
+                            const uint64_t ad = a_d0 + so, bd = b_d0 + so;
+                            umma_bf16_pair(d_tmem, ad, bd, idesc, acc);
+                            umma_bf16_pair(d_tmem, ad + 2, bd + b_step, idesc, 1u);
+                            umma_bf16_pair(d_tmem, ad + 4, bd + 2 * b_step, idesc, 1u);
+                            umma_bf16_pair(d_tmem, ad + 6, bd + 3 * b_step, idesc, 1u);
+                            acc = 1;
                         } else {
+                            const int kinstr = (krem + 15) / 16;
                             for (int ki = 0; ki < kinstr; ki++) {
-                                const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
-                                                         : smem_desc_sw128(sb + ki * 32, 16, 1024);
-                                umma_bf16_pair(d_tmem, smem_desc_sw128(sa + ki * 32, 16, 1024), bd, idesc, acc);
+                                umma_bf16_pair(d_tmem, a_d0 + so + 2 * ki, b_d0 + so + b_step * ki, idesc, acc);
                                 acc = 1;
                             }
                         }
-                        umma_commit_pair(smem_u32(&empty[stage]));
+                        umma_commit_pair(empty0 + stage * 8);
                         umma_commit_pair(peer_empty0 + stage * 8);
+                        if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
                     }
                 }
                 umma_commit_pair(smem_u32(&tfull[buf]));
