@@ -962,6 +962,201 @@ done:
     }
 }
 
+// ── CTA-pair kernel, 256 x BN pair tile, double-buffered accumulators, 128-wide k blocks ───────
+// As the kernel above, but a ring stage holds a 128-wide k block (three stages of 64 KB instead of six of 32 KB): the
+// issuing thread's barrier round (wait, two commits, loop) is paid once per EIGHT MMAs, as in the single-CTA 256-row
+// kernel, instead of once per four - a pair tile leaves that thread one MMA per 128 clocks to hide it in and the MMA
+// queue is shallow.  Plain epilogue only (no fused SwiGLU forms).
+template <int BN>
+struct Pair3Cfg {
+    static constexpr int STAGES = 3;
+    static constexpr int BK2 = 2 * BK;                              // a stage holds a 128-wide k block: 8 MMAs per barrier round
+    static constexpr uint32_t A_BYTES = 128 * BK2 * 2;              // two 64-column chunks of [128 rows][128 B]
+    static constexpr uint32_t B_BYTES = 128 * BK2 * 2;              // half tile, same shape (MN-major: two n chunks of [128 k][128 B])
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024 + 256 + 32768;
+};
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    seg_gemm_pair3_kernel(const __grid_constant__ SegGemmParams p) {
+    using C = Pair3Cfg<BN>;
+    constexpr int HALF = BN / 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    // behind the ring: two 2 KB epilogue staging tiles per epilogue warp (warps 2..9), then the barrier block
+    uint4* stage = reinterpret_cast<uint4*>(smem + C::STAGES * C::STAGE_BYTES) + ((threadIdx.x >> 5) >= 2 ? ((threadIdx.x >> 5) - 2) * 256 : 0);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES + kEpiStageBytes);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* tfull = empty + C::STAGES;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint32_t nchunk = 0;   // chunks this epilogue warp has staged so far (selects one of its two staging tiles)
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(&full[s], 2);      // one arrive.expect_tx from each CTA's producer
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], 16);   // eight epilogue warps in each CTA
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                  // the peer's barriers are initialised before anything arrives on them
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int m_tiles = (p.M + 255) / 256;
+    const int tile_n = BN;
+    const int n_tiles = (p.N + tile_n - 1) / tile_n;
+    const int total = m_tiles * n_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int s = 0; s < p.nseg; s++) {
+                prefetch_tensormap(&p.tmA[s]);
+                prefetch_tensormap(&p.tmB[s]);
+            }
+            uint32_t it = 0;
+            for (int tile = pair; tile < total; tile += npairs) {
+                const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, tile_n, p.group_m, p.group_n);
+                const int m0 = tc.m0 + int(rank) * 128, nh = tc.n0 + int(rank) * HALF;
+                for (int s = 0; s < p.nseg; s++) {
+                    const int nkb = (p.K[s] + C::BK2 - 1) / C::BK2;
+                    const bool b_mn = p.b_mn[s] != 0;
+                    for (int kb = 0; kb < nkb; kb++, it++) {
+                        const uint32_t stage = it % C::STAGES;
+                        const uint32_t ph = (it / C::STAGES) & 1u;
+                        if (!mbar_wait(&empty[stage], ph ^ 1u, abort_flag, p.status, DS_TIMEOUT_PRODUCER)) goto done;
+                        uint8_t* sa = smem + stage * C::STAGE_BYTES;
+                        uint8_t* sb = sa + C::A_BYTES;
+                        const uint32_t fbar = map_to_cta(smem_u32(&full[stage]), 0);
+                        const int k0 = kb * C::BK2;
+                        // boxes that start past K are filled with zeros and still count their bytes
+                        mbar_arrive_expect_tx_cluster(fbar, C::STAGE_BYTES);
+                        tma_load_2d_pair(sa, &p.tmA[s], fbar, k0, m0);                    // box {64, 128}
+                        tma_load_2d_pair(sa + 16384, &p.tmA[s], fbar, k0 + 64, m0);
+                        if (!b_mn) {
+                            tma_load_2d_pair(sb, &p.tmB[s], fbar, k0, nh);                // box {64, 128}
+                            tma_load_2d_pair(sb + 16384, &p.tmB[s], fbar, k0 + 64, nh);
+                        } else {                                                          // box {64 n, 64 k} x 4
+                            tma_load_2d_pair(sb, &p.tmB[s], fbar, nh, k0);
+                            tma_load_2d_pair(sb + 8192, &p.tmB[s], fbar, nh, k0 + 64);
+                            tma_load_2d_pair(sb + 16384, &p.tmB[s], fbar, nh + 64, k0);
+                            tma_load_2d_pair(sb + 16384 + 8192, &p.tmB[s], fbar, nh + 64, k0 + 64);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t peer_empty0 = map_to_cta(smem_u32(&empty[0]), 1), peer_tfull0 = map_to_cta(smem_u32(&tfull[0]), 1);
+            // One MMA covers 128 clocks of tensor work for the pair, so the issuing thread has ~128 clocks per MMA for
+            // everything else: descriptors are built once (stage 0) and advanced with one 64-bit add (the start-address
+            // field counts 16-byte units and never carries: shared-memory addresses stay below 256 KB).
+            const uint32_t s0 = smem_u32(smem);
+            const uint64_t a_d0 = smem_desc_sw128(s0, 16, 1024);
+            const uint64_t bk_d0 = smem_desc_sw128(s0 + C::A_BYTES, 16, 1024), bmn_d0 = smem_desc_sw128(s0 + C::A_BYTES, 16384, 1024);
+            const uint32_t empty0 = smem_u32(&empty[0]);
+            uint32_t lt = 0, stage = 0, ph = 0;
+            for (int tile = pair; tile < total; tile += npairs, lt++) {
+                const uint32_t buf = lt & 1u, use = lt >> 1;
+                if (!mbar_wait(&tempty[buf], (use & 1u) ^ 1u, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
+                tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                uint32_t acc = 0;
+                for (int s = 0; s < p.nseg; s++) {
+                    const int nkb = (p.K[s] + C::BK2 - 1) / C::BK2;
+                    const bool b_mn = p.b_mn[s] != 0;
+                    const uint32_t idesc = umma_idesc_bf16(256, BN, false, b_mn);
+                    const uint64_t b_d0 = b_mn ? bmn_d0 : bk_d0;
+                    // k advances by 16: K-major 32 B inside a 64-column chunk and 16 KB to the next chunk; MN-major 16 rows = 2 KB
+                    const uint64_t b_step = b_mn ? (2048u >> 4) : (32u >> 4), b_half = b_mn ? (4 * 2048u >> 4) : (16384u >> 4);
+                    for (int kb = 0; kb < nkb; kb++) {
+                        if (!mbar_wait(&full[stage], ph, abort_flag, p.status, DS_TIMEOUT_MMA)) goto done;
+                        tcgen05_fence_after_sync();
+                        const uint64_t so = uint64_t(stage * C::STAGE_BYTES) >> 4;
+                        const uint64_t ad = a_d0 + so, bd = b_d0 + so;
+                        const int krem = p.K[s] - kb * C::BK2;
+                        if (krem >= C::BK2) {
+                            umma_bf16_pair(d_tmem, ad, bd, idesc, acc);
+                            umma_bf16_pair(d_tmem, ad + 2, bd + b_step, idesc, 1u);
+                            umma_bf16_pair(d_tmem, ad + 4, bd + 2 * b_step, idesc, 1u);
+                            umma_bf16_pair(d_tmem, ad + 6, bd + 3 * b_step, idesc, 1u);
+                            umma_bf16_pair(d_tmem, ad + 1024, bd + b_half, idesc, 1u);
+                            umma_bf16_pair(d_tmem, ad + 1026, bd + b_half + b_step, idesc, 1u);
+                            umma_bf16_pair(d_tmem, ad + 1028, bd + b_half + 2 * b_step, idesc, 1u);
+                            umma_bf16_pair(d_tmem, ad + 1030, bd + b_half + 3 * b_step, idesc, 1u);
+                            acc = 1;
+                        } else {
+                            const int kinstr = (krem + 15) / 16;
+                            for (int ki = 0; ki < kinstr; ki++) {
+                                umma_bf16_pair(d_tmem, ad + (ki >> 2) * 1024 + (ki & 3) * 2, bd + (ki >> 2) * b_half + (ki & 3) * b_step, idesc, acc);
+                                acc = 1;
+                            }
+                        }
+                        umma_commit_pair(empty0 + stage * 8);
+                        umma_commit_pair(peer_empty0 + stage * 8);
+                        if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
+                    }
+                }
+                umma_commit_pair(smem_u32(&tfull[buf]));
+                umma_commit_pair(peer_tfull0 + buf * 8);
+            }
+        }
+    } else {
+        // eight epilogue warps per CTA: two per TMEM lane group, each draining half of the columns
+        const int lg = warp & 3;
+        const int eh = (warp - 2) >> 2;
+        const uint32_t tempty0 = map_to_cta(smem_u32(&tempty[0]), 0);
+        constexpr int NCH = BN / 32;
+        const int c_lo = eh * ((NCH + 1) / 2), c_hi = eh == 0 ? (NCH + 1) / 2 : NCH;
+        uint32_t lt = 0;
+        for (int tile = pair; tile < total; tile += npairs, lt++) {
+            const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, 256, tile_n, p.group_m, p.group_n);
+            const uint32_t buf = lt & 1u, use = lt >> 1;
+            if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, DS_TIMEOUT_EPILOGUE)) goto done;
+            tcgen05_fence_after_sync();
+            const int row = tc.m0 + int(rank) * 128 + lg * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * 256u + (uint32_t(lg * 32) << 16);
+            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, c_lo, c_hi, stage, nchunk);
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + buf * 8);
+        }
+    }
+
+done:
+    __syncwarp();
+    if (warp >= 2 && lane == 0) bulk_wait_all();   // this warp's output tiles have reached global memory
+    if (*abort_flag) {
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                  // neither CTA leaves while the other may still signal or read it
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
 // Fixed-order reduction of split-K partials: out (+)= sum_s ws[s][m][n]; optional transposed store.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, long split_stride, int M, int N,
                                      float* __restrict__ out, long ldo, int transpose, int accumulate) {
@@ -1019,6 +1214,21 @@ int launch_pair2(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int t
     const int grid = 2 * std::min(total_pair_tiles, ctx->sm_count / 2);
     seg_gemm_pair2_kernel<BN><<<grid, kGemmThreads, Pair2Cfg<BN>::SMEM, stream>>>(p);
     TA_LAUNCH_CHECK(ctx, "seg_gemm_pair2_kernel");
+    return TA_OK;
+}
+
+template <int BN>
+int launch_pair3(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int total_pair_tiles) {
+    static bool attr_set[64] = {};   // per-device, written on first use from the context's one host thread
+    const int dev = ctx->device & 63;
+    if (!attr_set[dev]) {
+        TA_CUDA(ctx, cudaFuncSetAttribute(seg_gemm_pair3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          int(Pair3Cfg<BN>::SMEM)));
+        attr_set[dev] = true;
+    }
+    const int grid = 2 * std::min(total_pair_tiles, ctx->sm_count / 2);
+    seg_gemm_pair3_kernel<BN><<<grid, kGemmThreads, Pair3Cfg<BN>::SMEM, stream>>>(p);
+    TA_LAUNCH_CHECK(ctx, "seg_gemm_pair3_kernel");
     return TA_OK;
 }
 
@@ -1130,6 +1340,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     // CTA-pair kernel (512 x 256 tiles over two SMs): same A boxes as the 256-row kernel, half-width B boxes.
     // Opt-in (ta_ctx_set_gemm_tuning): measured 3-7 % slower than the single-CTA 256-row kernel on the 7B shapes.
     const bool use_pair2 = ctx->gemm_pair == 2 && bn == 256 && tcfg.mh == 2 && out.split_k <= 1 && M >= 256 && (ctx->sm_count % 2) == 0;
+    const bool use_pair3 = ctx->gemm_pair == 3 && !dual && out.epi == 0 && bn == 256 && tcfg.mh == 2 && out.split_k <= 1 && M >= 256 && (ctx->sm_count % 2) == 0;
     const bool use_pair = ctx->gemm_pair == 1 && out.epi == 0 && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
     SegGemmParams p;
     std::memset(&p, 0, sizeof(p));
@@ -1142,7 +1353,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
             return fail(ctx, TA_ERR_INVALID, "seg_gemm: MN-major A needs M % 8 == 0");
         int rc;
         auto get_tmap_bf16 = out.no_host_state ? encode_tmap_bf16 : ta::get_tmap_bf16;
-        if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, uint32_t(use_pair2 ? 128 : tile_m), &p.tmA[s]);
+        if (!g.a_mn) rc = get_tmap_bf16(ctx, g.A, uint64_t(g.K), uint64_t(M), uint64_t(g.lda) * 2, 64, uint32_t(use_pair2 || use_pair3 ? 128 : tile_m), &p.tmA[s]);
         else         rc = get_tmap_bf16(ctx, g.A, uint64_t(M), uint64_t(g.K), uint64_t(g.lda) * 2, 64, 64, &p.tmA[s]);
         if (rc) return rc;
         if (dual) {
@@ -1152,7 +1363,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
             rc = get_tmap_bf16(ctx, g.B, kb_dim, uint64_t(N), uint64_t(g.ldb) * 2, 64, box_rows, &p.tmB[s]);
             if (!rc) rc = get_tmap_bf16(ctx, g.B2, kb_dim, uint64_t(N), uint64_t(g.ldb2) * 2, 64, box_rows, &p.tmB2[s]);
             p.k_half[s] = g.k_half;
-        } else if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(use_pair || use_pair2 ? bn / 2 : bn), &p.tmB[s]);
+        } else if (!g.b_mn) rc = get_tmap_bf16(ctx, g.B, uint64_t(g.K), uint64_t(N), uint64_t(g.ldb) * 2, 64, uint32_t(use_pair || use_pair2 || use_pair3 ? bn / 2 : bn), &p.tmB[s]);
         else         rc = get_tmap_bf16(ctx, g.B, uint64_t(N), uint64_t(g.K), uint64_t(g.ldb) * 2, 64, 64, &p.tmB[s]);
         if (rc) return rc;
         p.K[s] = g.K;
@@ -1203,7 +1414,9 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     }
     ProfScope prof(out.no_host_state ? nullptr : ctx, stream, bn >= 128 ? PROF_GEMM : PROF_GEMM_SKINNY, 2.0 * M * N * ksum);
     int rc;
-    if (use_pair2) {
+    if (use_pair3) {
+        rc = launch_pair3<256>(ctx, stream, p, ((M + 255) / 256) * n_tiles);
+    } else if (use_pair2) {
         rc = launch_pair2<256>(ctx, stream, p, ((M + 255) / 256) * n_tiles);
     } else if (use_pair) {
         rc = launch_pair<256>(ctx, stream, p, ((M + 511) / 512) * n_tiles);

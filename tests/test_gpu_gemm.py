@@ -109,12 +109,12 @@ def test_gemm_rejects_bad_arguments(ctx):
         ctx.call("ta_gemm_bf16", 128, 64, 64, 1.0, None, 64, 0, ptr(A), 64, 0, None, None, ptr(A), 64, stream_ptr())
 
 
-@pytest.mark.parametrize("pair_mode", [1, 2])
+@pytest.mark.parametrize("pair_mode", [1, 2, 3])
 @pytest.mark.parametrize("M,N,K,b_layout,extras", [(512, 256, 64, 0, False), (1064, 776, 520, 0, False), (1064, 776, 520, 1, False),
                                                      (2048, 1024, 1000, 0, True), (1536, 3584, 1024, 1, True), (300, 264, 4104, 0, True)])
 def test_cta_pair_kernel_matches_fp32_reference(ctx, M, N, K, b_layout, extras, pair_mode):
     """The CTA-pair kernels (tcgen05 cta_group::2 over two SMs; mode 1: 512 x 256 pair tiles, mode 2: 256 x 256 pair
-    tiles with double-buffered accumulators) against an FP32 torch product: K-major and MN-major B, ragged
+    tiles with double-buffered accumulators, mode 3: the same with 128-wide k blocks) against an FP32 torch product: K-major and MN-major B, ragged
     M / N / K, bias and residual."""
     ctx.call("ta_ctx_set_gemm_tuning", 256, 2, pair_mode)
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
