@@ -58,7 +58,9 @@ int ta_selftest_bounded_wait(ta_ctx* ctx, int limit_us, int* wait_returned_true,
 long ta_launch_count(const ta_ctx* ctx);
 /* Experiment knob, no counterpart in the reference: force the GEMM tile (tile_n in {64,128,224,256},
  * tile_m_halves 1 = 128-row or 2 = 256-row tiles; 0,0 = the built-in cost model) and / or select a
- * CTA-pair kernel for 256-wide tiles (cta_pair 1: 512 x 256 pair tiles, 2: 256 x 256 with double-buffered accumulators, 3: as 2 with 128-wide k blocks).  Results are bit-identical for every choice.
+ * kernel for 256-wide tiles (cta_pair 0: the library's choice - the 256 x 256 CTA-pair kernel of mode 3 where the device
+ * can keep a pair resident on every two SMs; -1: single-CTA kernels only; 1: 512 x 256 pair tiles; 2: 256 x 256 pair tiles
+ * with double-buffered accumulators; 3: as 2 with 128-wide k blocks).  Results are bit-identical for every choice.
  * Threading: a context, and every object created from it, belongs to ONE host thread at a time (the
  * reference's Device is single-threaded too); the library keeps per-device launch attributes and the
  * static-scratch address in unsynchronised process-wide state that is written on first use. */

@@ -173,6 +173,7 @@ int ta_ctx_set_gemm_tuning(ta_ctx* ctx, int tile_n, int tile_m_halves, int cta_p
     if (!none && !ok) return ta::fail(ctx, TA_ERR_INVALID, "gemm tuning: tile_n in {64,128,224,256}, halves 1 or 2 (2 needs tile_n >= 224)");
     ctx->gemm_force_bn = tile_n;
     ctx->gemm_force_mh = tile_m_halves;
+    if (cta_pair < -1 || cta_pair > 3) return ta::fail(ctx, TA_ERR_INVALID, "gemm tuning: cta_pair in {-1, 0, 1, 2, 3}");
     ctx->gemm_pair = cta_pair;
     return TA_OK;
 }

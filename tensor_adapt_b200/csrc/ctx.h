@@ -50,7 +50,7 @@ struct ta_ctx {
     // GEMM tile overrides for experiments (ta_ctx_set_gemm_tuning); 0 = let the cost model choose
     int gemm_force_bn = 0, gemm_force_mh = 0;
     int gemm_group_m = 0, gemm_group_n = 0;   // raster override (0 = built-in choice)
-    int gemm_pair = 0;              // 256-wide tiles: 1 = CTA-pair kernel with 512 x 256 pair tiles, 2 = 256 x 256 pair tiles
+    int gemm_pair = 0;              // 256-wide tiles: 0 = library's choice, -1 = single-CTA kernel only, 1 / 2 / 3 = that CTA-pair kernel
     // optional per-kernel-class timing with CUDA events (off by default; see ta_profile_*)
     bool profiling = false;
     struct ProfRec { int cls; double work; cudaEvent_t e0, e1; };

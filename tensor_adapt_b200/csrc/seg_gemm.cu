@@ -1217,16 +1217,35 @@ int launch_pair2(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int t
     return TA_OK;
 }
 
+// How many CTA pairs of the mode-3 kernel the device keeps resident at once (0: the query failed).  The kernel hands
+// tiles to pairs statically, so a launch must not hold more pairs than that: the rest would start when the first ones
+// END and double the launch time.  Cached per device, written on first use from the context's one host thread.
+template <int BN>
+int pair3_resident_pairs(ta_ctx* ctx) {
+    static int resident[64] = {};
+    static bool known[64] = {};
+    const int dev = ctx->device & 63;
+    if (!known[dev]) {
+        known[dev] = true;
+        if (cudaFuncSetAttribute(seg_gemm_pair3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(Pair3Cfg<BN>::SMEM)) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(unsigned(ctx->sm_count & ~1));
+            cfg.blockDim = dim3(kGemmThreads);
+            cfg.dynamicSmemBytes = Pair3Cfg<BN>::SMEM;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, seg_gemm_pair3_kernel<BN>, &cfg) == cudaSuccess) resident[dev] = n;
+        }
+        (void)cudaGetLastError();
+    }
+    return resident[dev];
+}
+
 template <int BN>
 int launch_pair3(ta_ctx* ctx, cudaStream_t stream, const SegGemmParams& p, int total_pair_tiles) {
-    static bool attr_set[64] = {};   // per-device, written on first use from the context's one host thread
-    const int dev = ctx->device & 63;
-    if (!attr_set[dev]) {
-        TA_CUDA(ctx, cudaFuncSetAttribute(seg_gemm_pair3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          int(Pair3Cfg<BN>::SMEM)));
-        attr_set[dev] = true;
-    }
-    const int grid = 2 * std::min(total_pair_tiles, ctx->sm_count / 2);
+    const int resident = pair3_resident_pairs<BN>(ctx);
+    if (resident <= 0) return fail(ctx, TA_ERR_CUDA, "seg_gemm: the CTA-pair kernel cannot be resident on this device");
+    const int grid = 2 * std::min(total_pair_tiles, std::min(resident, ctx->sm_count / 2));
     seg_gemm_pair3_kernel<BN><<<grid, kGemmThreads, Pair3Cfg<BN>::SMEM, stream>>>(p);
     TA_LAUNCH_CHECK(ctx, "seg_gemm_pair3_kernel");
     return TA_OK;
@@ -1333,14 +1352,25 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
             return fail(ctx, TA_ERR_INVALID, "seg_gemm: the SwiGLU backward epilogue needs the forward's gate and up");
         }
     }
-    const TileChoice tcfg = dual              ? TileChoice{256, 2}
-                            : out.split_k > 1 ? TileChoice{pick_bn(N), 1}
-                                              : pick_tile(ctx, M, N, dual ? 2 * ksum_all : ksum_all, any_a_mn);
+    TileChoice tcfg = dual              ? TileChoice{256, 2}
+                      : out.split_k > 1 ? TileChoice{pick_bn(N), 1}
+                                        : pick_tile(ctx, M, N, dual ? 2 * ksum_all : ksum_all, any_a_mn);
+    // The 256 x 256 CTA-pair kernel with 128-wide k blocks (mode 3) hides its epilogue behind the next main loop, which
+    // pays when the contraction is short: measured against the best single-CTA tile on 16384-row problems it is
+    // +4 % (N 18944, K 3584), +7-8 % (N 3584, K 3584), +4 % (N 512), +5 % (N 4608), but -2 to -5 % at K 18944, where
+    // the epilogue is a small share and 74 concurrent tiles re-stream more panels than 148.  It is the library's
+    // choice for short contractions when every two SMs can hold a pair at once; cta_pair -1 switches it off.
+    const bool pair3_shape = !dual && out.epi == 0 && out.split_k <= 1 && !any_a_mn && M >= 256 && (ctx->sm_count % 2) == 0;
+    if (ctx->gemm_pair == 0 && !ctx->gemm_force_bn && pair3_shape && N >= 256 && ksum_all <= 8192 &&
+        pair3_resident_pairs<256>(ctx) >= ctx->sm_count / 2)
+        tcfg = TileChoice{256, 3};
+    const bool auto_pair3 = tcfg.mh == 3;
+    if (auto_pair3) tcfg.mh = 2;
     const int bn = tcfg.bn, tile_m = 128 * tcfg.mh;
     // CTA-pair kernel (512 x 256 tiles over two SMs): same A boxes as the 256-row kernel, half-width B boxes.
     // Opt-in (ta_ctx_set_gemm_tuning): measured 3-7 % slower than the single-CTA 256-row kernel on the 7B shapes.
     const bool use_pair2 = ctx->gemm_pair == 2 && bn == 256 && tcfg.mh == 2 && out.split_k <= 1 && M >= 256 && (ctx->sm_count % 2) == 0;
-    const bool use_pair3 = ctx->gemm_pair == 3 && !dual && out.epi == 0 && bn == 256 && tcfg.mh == 2 && out.split_k <= 1 && M >= 256 && (ctx->sm_count % 2) == 0;
+    const bool use_pair3 = pair3_shape && bn == 256 && tcfg.mh == 2 && (auto_pair3 || ctx->gemm_pair == 3);
     const bool use_pair = ctx->gemm_pair == 1 && out.epi == 0 && tcfg.mh == 2 && bn == 256 && out.split_k <= 1 && M >= 512 && (ctx->sm_count % 2) == 0;
     SegGemmParams p;
     std::memset(&p, 0, sizeof(p));

@@ -214,7 +214,7 @@ def main():
                 s.add_argument("--" + k, type=int, default=v)
             s.add_argument("--b-layout", type=int, default=0)
             s.add_argument("--tile", default="", help='force a tile "BN,MH" (experiment knob)')
-            s.add_argument("--pair", type=int, default=0, help="CTA-pair kernel: 0 off, 1 = 512x256 pair tiles, 2 = 256x256, 3 = 256x256 with 128-wide k blocks")
+            s.add_argument("--pair", type=int, default=0, help="256-wide tiles: 0 = library's choice, -1 = single-CTA kernel, 1 = 512x256 pair tiles, 2 = 256x256 pairs, 3 = 256x256 pairs with 128-wide k blocks")
             s.add_argument("--raster", default="", help='tile order "GROUP_M,GROUP_N" (experiment knob; 0 = default)')
         elif name == "kmeans":
             for k, v in (("N", 2048), ("D", 512), ("k", 8)):
