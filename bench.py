@@ -59,9 +59,9 @@ SHAPES = {
 # `python -m tensor_adapt_b200.microbench gemm --M 16384 --N .. --K ..` (summary under profiles/), with the
 # launches of each shape per layer pass; `roofline.traffic` is their launch-weighted mean.
 NCU_GEMM_TRAFFIC_7B = {
-    "16384x18944x3584 (gate, up, dX of down)": (1.391e9, 3),
-    "16384x3584x18944 (down, halves of dX of gate+up)": (2.163e9, 3),
-    "16384x3584x3584 (q, o and their dX)": (0.278e9, 4),
+    "16384x18944x3584 (gate, up, dX of down; CTA-pair kernel)": (1.308e9, 3),
+    "16384x3584x18944 (down, halves of dX of gate+up; 256 x 224 single-CTA tiles)": (1.911e9, 3),
+    "16384x3584x3584 (q, o and their dX; CTA-pair kernel)": (0.244e9, 4),
 }
 
 
@@ -372,7 +372,7 @@ def main():
                          "traffic_note": ("bytes per launch, launch-weighted mean of ncu captures of the three dominant shapes; "
                                           "algorithmic operand + output bytes of the same mix: 0.63e9" if args.config == "qwen2-7b" else None),
                          "peak_source": f"{src} bf16_tflops_sustained (kernel timed inside a long step)",
-                         "kernel": "seg_gemm_kernel (tiles >= 128 wide)", "kernel_launches": int(nl[0]),
+                         "kernel": "seg_gemm_kernel + seg_gemm_pair3_kernel (tiles >= 128 wide)", "kernel_launches": int(nl[0]),
                          "kernel_ms_per_step": pm[0], "kernel_share_of_step": pm[0] / ms_dev,
                          "step_tflops_per_gpu": step_tf, "step_frac_of_burst_peak": step_tf / peaks["bf16_tflops"],
                          "step_frac_of_sustained_peak": step_tf / peak,
