@@ -313,8 +313,9 @@ int ta_trainer_init_random(ta_trainer* tr, unsigned long long seed, float std);
  * dtype: 0 = FP32, 1 = BF16. pitch is the row pitch in elements. */
 int ta_trainer_tensor(ta_trainer* tr, const char* name, void** dev_ptr, long* rows, long* cols, long* pitch, int* dtype);
 /* Switches of the step's fusions, for A/B comparisons: "fuse_swiglu" (1: SwiGLU forward / backward run inside the
- * gate-up and down-dX GEMM epilogues; default 0: separate silu_mul kernels as the reference has them, which is the
- * faster arrangement with the current tile shapes).  No reference counterpart. */
+ * gate-up and down-dX GEMM epilogues; 0: separate silu_mul kernels as the reference has them; -1, the default: fused
+ * where the CTA-pair GEMM kernel carries those launches and hides the epilogue, separate otherwise).  The forward is
+ * bit-identical either way; the fused backward skips one BF16 rounding of d_act.  No reference counterpart. */
 int ta_trainer_set_option(ta_trainer* tr, const char* name, int value);
 /* Re-derive the BF16 working copies from the FP32 masters (after masters were uploaded). */
 int ta_trainer_sync_working(ta_trainer* tr);

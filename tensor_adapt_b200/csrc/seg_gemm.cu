@@ -966,7 +966,7 @@ done:
 // As the kernel above, but a ring stage holds a 128-wide k block (three stages of 64 KB instead of six of 32 KB): the
 // issuing thread's barrier round (wait, two commits, loop) is paid once per EIGHT MMAs, as in the single-CTA 256-row
 // kernel, instead of once per four - a pair tile leaves that thread one MMA per 128 clocks to hide it in and the MMA
-// queue is shallow.  Plain epilogue only (no fused SwiGLU forms).
+// queue is shallow.
 template <int BN>
 struct Pair3Cfg {
     static constexpr int STAGES = 3;
@@ -1022,7 +1022,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const uint32_t tmem_base = *tmem_slot;
 
     const int m_tiles = (p.M + 255) / 256;
-    const int tile_n = BN;
+    const int tile_n = p.dual ? 128 : BN;     // dual tiles: 128 gate columns + the 128 matching up columns
     const int n_tiles = (p.N + tile_n - 1) / tile_n;
     const int total = m_tiles * n_tiles;
 
@@ -1031,6 +1031,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             for (int s = 0; s < p.nseg; s++) {
                 prefetch_tensormap(&p.tmA[s]);
                 prefetch_tensormap(&p.tmB[s]);
+                if (p.dual) prefetch_tensormap(&p.tmB2[s]);
             }
             uint32_t it = 0;
             for (int tile = pair; tile < total; tile += npairs) {
@@ -1051,6 +1052,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         mbar_arrive_expect_tx_cluster(fbar, C::STAGE_BYTES);
                         tma_load_2d_pair(sa, &p.tmA[s], fbar, k0, m0);                    // box {64, 128}
                         tma_load_2d_pair(sa + 16384, &p.tmA[s], fbar, k0 + 64, m0);
+                        if (p.dual) {
+                            if (!p.k_half[s]) {
+                                // main segment: this CTA supplies one half of the N = 256 operand - rank 0 the gate rows,
+                                // rank 1 the matching up rows (boxes {64, 128} of its own tensor map)
+                                const CUtensorMap* tb = rank ? &p.tmB2[s] : &p.tmB[s];
+                                tma_load_2d_pair(sb, tb, fbar, k0, tc.n0);
+                                tma_load_2d_pair(sb + 16384, tb, fbar, k0 + 64, tc.n0);
+                            } else {
+                                // rank-r segment, A = [h_gate | h_up]: per 64-wide half of the stage two N = 128 products,
+                                // each CTA supplies 64 rows of both adapters (boxes {64, 64})
+#pragma unroll
+                                for (int j = 0; j < 2; j++) {
+                                    const int kk = k0 + 64 * j;
+                                    tma_load_2d_pair(sb + j * 16384, &p.tmB[s], fbar, kk, tc.n0 + int(rank) * 64);
+                                    tma_load_2d_pair(sb + j * 16384 + 8192, &p.tmB2[s], fbar, max(kk - p.k_half[s], 0), tc.n0 + int(rank) * 64);
+                                }
+                            }
+                            continue;
+                        }
                         if (!b_mn) {
                             tma_load_2d_pair(sb, &p.tmB[s], fbar, k0, nh);                // box {64, 128}
                             tma_load_2d_pair(sb + 16384, &p.tmB[s], fbar, k0 + 64, nh);
@@ -1094,7 +1114,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         const uint64_t so = uint64_t(stage * C::STAGE_BYTES) >> 4;
                         const uint64_t ad = a_d0 + so, bd = b_d0 + so;
                         const int krem = p.K[s] - kb * C::BK2;
-                        if (krem >= C::BK2) {
+                        if (p.dual && p.k_half[s]) {
+                            const uint32_t sa = s0 + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+                            const uint32_t idesc_h = umma_idesc_bf16(256, 128, false, false);
+                            for (int j = 0; j < 2; j++)
+                                for (int ki = 0; ki < 4; ki++) {
+                                    const int c = kb * C::BK2 + j * 64 + ki * 16;
+                                    if (c >= p.K[s]) break;
+                                    const DualStep ds = dual_step(c, p.k_half[s], 2 * kb + j);
+                                    umma_bf16_pair(d_tmem + ds.half * 128, smem_desc_sw128(sa + j * 16384 + ki * 32, 16, 1024),
+                                                   smem_desc_sw128(sb + j * 16384 + ds.half * 8192 + ds.b_off, 16, 1024), idesc_h, acc);
+                                }
+                        } else if (krem >= C::BK2) {
                             umma_bf16_pair(d_tmem, ad, bd, idesc, acc);
                             umma_bf16_pair(d_tmem, ad + 2, bd + b_step, idesc, 1u);
                             umma_bf16_pair(d_tmem, ad + 4, bd + 2 * b_step, idesc, 1u);
@@ -1135,7 +1166,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             tcgen05_fence_after_sync();
             const int row = tc.m0 + int(rank) * 128 + lg * 32 + lane;
             const uint32_t taddr = tmem_base + buf * 256u + (uint32_t(lg * 32) << 16);
-            epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, c_lo, c_hi, stage, nchunk);
+            if (p.epi == 1)      epilogue_swiglu_fwd(p, taddr, row, tc.n0, eh * 2, eh * 2 + 2, stage);
+            else if (p.epi == 2) epilogue_swiglu_bwd(p, taddr, row, tc.n0, c_lo, c_hi, stage);
+            else                 epilogue_chunks<32>(p, taddr, row, row < p.M, tc.n0, 0, c_lo, c_hi, stage, nchunk);
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0 + buf * 8);
@@ -1319,6 +1352,11 @@ size_t tokens_gemm_ws_bytes_max(const ta_ctx* ctx, int M, int N) {
 
 bool seg_gemm_supports_swiglu(const ta_ctx* ctx, int M) { return ctx && M >= 256; }
 
+bool seg_gemm_swiglu_pays(ta_ctx* ctx, int M) {
+    return seg_gemm_supports_swiglu(ctx, M) && ctx->gemm_pair == 0 && !ctx->gemm_force_bn && (ctx->sm_count % 2) == 0 &&
+           pair3_resident_pairs<256>(ctx) >= ctx->sm_count / 2;
+}
+
 int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* segs, int nseg, const GemmOut& out) {
     if (!ctx) return TA_ERR_INVALID;
     if (nseg < 1 || nseg > kMaxSegments) return fail(ctx, TA_ERR_INVALID, "seg_gemm: 1..6 segments");
@@ -1360,7 +1398,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
     // +4 % (N 18944, K 3584), +7-8 % (N 3584, K 3584), +4 % (N 512), +5 % (N 4608), but -2 to -5 % at K 18944, where
     // the epilogue is a small share and 74 concurrent tiles re-stream more panels than 148.  It is the library's
     // choice for short contractions when every two SMs can hold a pair at once; cta_pair -1 switches it off.
-    const bool pair3_shape = !dual && out.epi == 0 && out.split_k <= 1 && !any_a_mn && M >= 256 && (ctx->sm_count % 2) == 0;
+    const bool pair3_shape = out.split_k <= 1 && !any_a_mn && M >= 256 && (ctx->sm_count % 2) == 0;
     if (ctx->gemm_pair == 0 && !ctx->gemm_force_bn && pair3_shape && N >= 256 && ksum_all <= 8192 &&
         pair3_resident_pairs<256>(ctx) >= ctx->sm_count / 2)
         tcfg = TileChoice{256, 3};
@@ -1389,7 +1427,7 @@ int seg_gemm(ta_ctx* ctx, cudaStream_t stream, int M, int N, const GemmSegment* 
         if (dual) {
             // gate / up operand pair: 128-row boxes (64-row ones for a rank-r segment on the CTA-pair kernel)
             const uint64_t kb_dim = g.k_half ? uint64_t(g.k_half) : uint64_t(g.K);
-            const uint32_t box_rows = (g.k_half && use_pair2) ? 64u : 128u;
+            const uint32_t box_rows = (g.k_half && (use_pair2 || use_pair3)) ? 64u : 128u;
             rc = get_tmap_bf16(ctx, g.B, kb_dim, uint64_t(N), uint64_t(g.ldb) * 2, 64, box_rows, &p.tmB[s]);
             if (!rc) rc = get_tmap_bf16(ctx, g.B2, kb_dim, uint64_t(N), uint64_t(g.ldb2) * 2, 64, box_rows, &p.tmB2[s]);
             p.k_half[s] = g.k_half;

@@ -59,6 +59,11 @@ struct GemmOut {
 
 // Whether seg_gemm can run the fused SwiGLU forms for this many rows (they need the 256-row tile kernels).
 bool seg_gemm_supports_swiglu(const ta_ctx* ctx, int M);
+// Whether they are also the FASTER arrangement: true when the library's own choice for these launches is the CTA-pair
+// kernel, whose epilogue runs under the next tile's main loop (16384 x 3584 x 18944: forward 2.98 ms against 3.17 ms for
+// two GEMMs + silu_mul_fwd, backward 1.86 against 2.10 ms); on the single-CTA kernels the epilogue is exposed and the
+// fused forms lose (3.63 / 2.38 ms).
+bool seg_gemm_swiglu_pays(ta_ctx* ctx, int M);
 
 // Split count the token-contracted gradient GEMM (M x N output, K tokens) should use, and the bytes
 // of partials that many splits need.

@@ -223,7 +223,7 @@ int run_micro(ta_trainer* t, int Bm, int T, float inv_count, bool exchange) {
     const int BT = Bm * T, H = c.hidden, I = c.intermediate, qd = c.q_heads * c.head_dim, kv = c.kv_heads * c.head_dim;
     const int Lyr = c.layers;
     // SwiGLU folded into the GEMM epilogues (no act / d_act round trips) whenever the 256-row tile kernels apply
-    const bool swiglu_fused = t->fuse_swiglu && seg_gemm_supports_swiglu(ctx, BT);
+    const bool swiglu_fused = t->fuse_swiglu < 0 ? seg_gemm_swiglu_pays(ctx, BT) : (t->fuse_swiglu != 0 && seg_gemm_supports_swiglu(ctx, BT));
 
     // ── forward ────────────────────────────────────────────────────────────
     RC(ta_embed_fwd(ctx, t->embed, t->tok, t->cache[0].r_in, BT, H, s));
@@ -615,7 +615,7 @@ int ta_trainer_tensor(ta_trainer* t, const char* name, void** dev_ptr, long* row
 
 int ta_trainer_set_option(ta_trainer* t, const char* name, int value) {
     if (!t || !name) return TA_ERR_INVALID;
-    if (!std::strcmp(name, "fuse_swiglu")) { t->fuse_swiglu = value != 0; return TA_OK; }
+    if (!std::strcmp(name, "fuse_swiglu")) { t->fuse_swiglu = value < 0 ? -1 : (value != 0); return TA_OK; }
     return fail(t->ctx, TA_ERR_INVALID, std::string("trainer_set_option: unknown option ") + name);
 }
 

@@ -82,7 +82,7 @@ struct ta_trainer {
     // SwiGLU forward / backward inside the gate-up / down-dX GEMM epilogues.  Off by default: the 256-row tiles use
     // all of tensor memory, so their epilogue is not overlapped and the extra epilogue work costs more than the
     // separate HBM-bound kernels it removes (measured: 3.66 vs 3.27 ms forward, 2.30 vs 2.20 ms backward per layer).
-    bool fuse_swiglu = false;
+    int fuse_swiglu = -1;           // 1 / 0: SwiGLU inside the GEMM epilogues or as separate kernels; -1: whichever is faster here
     int* tok = nullptr;
     int* tgt = nullptr;
     int logit_rows = 0;       // rows of the lm-head chunk buffer

@@ -23,7 +23,7 @@ def _bf(x):
     return x.to(torch.bfloat16).float()
 
 
-@pytest.mark.parametrize("pair", [0, 2])
+@pytest.mark.parametrize("pair", [-1, 0, 2, 3])
 @pytest.mark.parametrize("BT,H,I,rank", [(512, 256, 384, 16), (1064, 520, 1000, 16), (768, 896, 4864, 64), (300, 128, 136, 32),
                                           (640, 256, 512, 0), (2048, 1536, 2048, 48)])
 def test_fused_gate_up_swiglu_forward(ctx, BT, H, I, rank, pair):
@@ -53,7 +53,7 @@ def test_fused_gate_up_swiglu_forward(ctx, BT, H, I, rank, pair):
     assert (act.float() - a_ref).abs().max() <= 2.0 ** -8 * a_ref.abs().max() + 1e-6
 
 
-@pytest.mark.parametrize("pair", [0, 2])
+@pytest.mark.parametrize("pair", [-1, 0, 2, 3])
 @pytest.mark.parametrize("BT,H,I,rank", [(512, 256, 384, 16), (1064, 520, 1000, 16), (768, 896, 4864, 0), (300, 128, 136, 32),
                                           (100, 64, 72, 16)])
 def test_fused_down_backward_swiglu(ctx, BT, H, I, rank, pair):
