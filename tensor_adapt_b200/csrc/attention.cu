@@ -36,6 +36,8 @@ struct AttnParams {
     __nv_bfloat16* out3;       // dkv: dV
     float* lse;                // [B*Hq*T]
     const float* delta;        // [B*Hq*T]
+    int kv_parts;              // dkv: CTAs per (key tile, KV head, batch), each over a share of the group's query heads
+    float* part;               // dkv, kv_parts > 1: FP32 partial sums [2 (dK, dV)][kv_parts][B*T][Hkv*hd]
     int B, T, Hq, Hkv;
     float scale, scale_log2;
     int* status;
@@ -693,10 +695,15 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dkv_kernel(const __grid_const
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hbk = p.Hkv * p.B;
-    const int kt = int(blockIdx.x) / hbk;   // key tile 0 has the most work: all its CTAs start first
-    const int hk = (int(blockIdx.x) % hbk) % p.Hkv, b = (int(blockIdx.x) % hbk) / p.Hkv;
-    const int G = p.Hq / p.Hkv;
+    const int hbk = p.Hkv * p.B, hbkp = hbk * p.kv_parts;
+    const int kt = int(blockIdx.x) / hbkp;   // key tile 0 has the most work: all its CTAs start first
+    const int part = (int(blockIdx.x) % hbkp) % p.kv_parts, hb = (int(blockIdx.x) % hbkp) / p.kv_parts;
+    const int hk = hb % p.Hkv, b = hb / p.Hkv;
+    const int Gall = p.Hq / p.Hkv;
+    // with few (key tile, KV head, batch) triples the launch is as long as its heaviest CTA: the group's query heads
+    // are then shared out over kv_parts CTAs whose FP32 partial sums a second kernel adds up in a fixed order
+    const int g_lo = part * Gall / p.kv_parts, G = (part + 1) * Gall / p.kv_parts - g_lo;
+    const int h_lo = hk * Gall + g_lo;
     const int nq64 = (p.T + 63) / 64;
     const int per_head = nq64 - 2 * kt;      // query sub-tiles 2*kt .. nq64-1 can see these keys
     const int iters = G * per_head;
@@ -724,7 +731,7 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dkv_kernel(const __grid_const
             load_tile<HD>(smem + OFF_K, 16384, &p.tmK, kv_full, hk * HD, b * p.T + kv0);
             load_tile<HD>(smem + OFF_V, 16384, &p.tmV, kv_full, hk * HD, b * p.T + kv0);
             for (int it = 0; it < iters; it++) {
-                const int h = hk * G + it / per_head, qs = 2 * kt + it % per_head, st = it % QST;
+                const int h = h_lo + it / per_head, qs = 2 * kt + it % per_head, st = it % QST;
                 ATT_WAIT(&qdo_empty[st], ((it / QST) & 1) ^ 1u, DS_TIMEOUT_PRODUCER);
                 mbar_arrive_expect_tx(&qdo_full[st], 2 * TB64);
                 load_tile<HD>(smem + OFF_Q + st * TB64, 8192, &p.tmQ64, &qdo_full[st], h * HD, b * p.T + qs * 64);
@@ -775,7 +782,7 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dkv_kernel(const __grid_const
             for (int k = 0; k < 2; k++) {
                 fl[k] = INFINITY; fd[k] = 0.f;
                 if (it < iters) {
-                    const int h = hk * G + it / per_head, q = (2 * kt + it % per_head) * 64 + k * 32 + lane;
+                    const int h = h_lo + it / per_head, q = (2 * kt + it % per_head) * 64 + k * 32 + lane;
                     if (q < p.T) {
                         const size_t si = (size_t(b) * p.Hq + h) * p.T + q;
                         fl[k] = p.lse[si] * kLog2e; fd[k] = p.delta[si];
@@ -849,12 +856,20 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_dkv_kernel(const __grid_const
         for (int which = grp; which <= grp; which++) {   // group 0 stores dV, group 1 stores dK
             __nv_bfloat16* orow = (which == 0 ? p.out3 : p.out2) + ro;
             const uint32_t ta = (which == 0 ? TM_DV : TM_DK) + lane_addr;
+            // partial sums: [dK | dV][part][token][Hkv*hd] FP32
+            float* prow = p.kv_parts > 1 ? p.part + ((size_t(which == 0 ? 1 : 0) * p.kv_parts + part) * p.B * p.T + size_t(b) * p.T + kv_idx) *
+                                                        (size_t(p.Hkv) * HD) + hk * HD
+                                         : nullptr;
 #pragma unroll
             for (int c = 0; c < HD / 32; c++) {
                 uint32_t r[32];
                 tmem_ld_x32(ta + c * 32, r);
                 tmem_ld_wait();
-                if (ok) {
+                if (ok && prow) {
+#pragma unroll
+                    for (int g = 0; g < 8; g++)
+                        *reinterpret_cast<uint4*>(prow + c * 32 + g * 4) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+                } else if (ok) {
 #pragma unroll
                     for (int g = 0; g < 4; g++) {
                         uint32_t w[4];
@@ -873,6 +888,24 @@ done:
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == 1) { tcgen05_fence_after_sync(); tmem_dealloc(tmem, 512); }
+}
+
+// dK / dV from the partial sums of a head-split dK/dV launch: parts added in index order, one rounding to BF16.
+__global__ void __launch_bounds__(256) attn_dkv_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dK,
+                                                               __nv_bfloat16* __restrict__ dV, long n, int parts) {
+    const long i = (blockIdx.x * long(blockDim.x) + threadIdx.x) * 4;
+    if (i >= n) return;
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+        const float* src = part + size_t(w) * parts * n + i;
+        float4 a = *reinterpret_cast<const float4*>(src);
+        for (int q = 1; q < parts; q++) {
+            const float4 v = *reinterpret_cast<const float4*>(src + size_t(q) * n);
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        uint2 o = make_uint2(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w));
+        *reinterpret_cast<uint2*>((w == 0 ? dK : dV) + i) = o;
+    }
 }
 
 template <int HD> constexpr size_t fwd_smem() { return 5 * Tile<HD>::BYTES + 2 * 32768 + 256 + 1024; }
@@ -946,11 +979,21 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
         return fail(ctx, TA_ERR_INVALID, "flash_attn_bwd: null argument");
     if (int rc = check_shape(ctx, B, T, Hq, Hkv, head_dim)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int nt = (T + 127) / 128;
+    // dK/dV launch: one CTA per (key tile, KV head, batch); when that is too few to fill the device twice over, the
+    // query heads of a group are shared out over several CTAs (FP32 partials in the workspace, fixed-order reduce)
+    const int ctas = nt * Hkv * B, G = Hq / Hkv;
+    const int kv_parts = ctas >= 2 * ctx->sm_count ? 1 : std::min(G, (2 * ctx->sm_count + ctas - 1) / ctas);
+    const size_t n_kv = size_t(B) * T * Hkv * head_dim;
+    const size_t delta_bytes = delta_scratch ? 0 : ((size_t(B) * Hq * T * sizeof(float) + 255) & ~size_t(255));
+    const size_t part_bytes = kv_parts > 1 ? 2 * size_t(kv_parts) * n_kv * sizeof(float) : 0;
     float* delta = delta_scratch;
-    if (!delta) {
+    float* part = nullptr;
+    if (delta_bytes + part_bytes) {
         void* ws = nullptr;
-        if (int rc = get_workspace(ctx, size_t(B) * Hq * T * sizeof(float), &ws)) return rc;
-        delta = static_cast<float*>(ws);
+        if (int rc = get_workspace(ctx, delta_bytes + part_bytes, &ws)) return rc;
+        if (!delta) delta = static_cast<float*>(ws);
+        part = reinterpret_cast<float*>(static_cast<char*>(ws) + delta_bytes);
     }
     attn_delta_kernel<<<unsigned(std::min<long>((long(B) * T + 7) / 8, long(ctx->sm_count) * 16)), 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(out), delta, B, T, Hq, head_dim);
@@ -965,23 +1008,28 @@ int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* 
     if (int rc = get_tmap_bf16(ctx, dQ, uint64_t(Hq) * head_dim, uint64_t(B) * T, uint64_t(Hq) * head_dim * 2, 64, 32, &p.tmOut)) return rc;
     p.out2 = static_cast<__nv_bfloat16*>(dK);
     p.out3 = static_cast<__nv_bfloat16*>(dV);
-    const int nt = (T + 127) / 128;
+    p.kv_parts = kv_parts; p.part = part;
     // algorithmic count: five contractions (S, dP, dV, dK, dQ) over half the square
     ProfScope prof(ctx, s, PROF_ATTN_BWD, 5.0 * 2.0 * B * Hq * double(T) * T * head_dim * 0.5);
     if (head_dim == 128) {
         if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<128>, dkv_smem<128>())) return rc;
-        attn_bwd_dkv_kernel<128><<<dim3(nt * Hkv * B), 320, dkv_smem<128>(), s>>>(p);
+        attn_bwd_dkv_kernel<128><<<dim3(nt * Hkv * B * kv_parts), 320, dkv_smem<128>(), s>>>(p);
         TA_LAUNCH_CHECK(ctx, "attn_bwd_dkv_kernel");
         if (int rc = set_smem(ctx, attn_bwd_dq_kernel<128>, dq_smem<128>())) return rc;
         attn_bwd_dq_kernel<128><<<dim3(nt * Hq * B), 320, dq_smem<128>(), s>>>(p);
     } else {
         if (int rc = set_smem(ctx, attn_bwd_dkv_kernel<64>, dkv_smem<64>())) return rc;
-        attn_bwd_dkv_kernel<64><<<dim3(nt * Hkv * B), 320, dkv_smem<64>(), s>>>(p);
+        attn_bwd_dkv_kernel<64><<<dim3(nt * Hkv * B * kv_parts), 320, dkv_smem<64>(), s>>>(p);
         TA_LAUNCH_CHECK(ctx, "attn_bwd_dkv_kernel");
         if (int rc = set_smem(ctx, attn_bwd_dq_kernel<64>, dq_smem<64>())) return rc;
         attn_bwd_dq_kernel<64><<<dim3(nt * Hq * B), 320, dq_smem<64>(), s>>>(p);
     }
     TA_LAUNCH_CHECK(ctx, "attn_bwd_dq_kernel");
+    if (kv_parts > 1) {
+        attn_dkv_reduce_kernel<<<unsigned((n_kv / 4 + 255) / 256), 256, 0, s>>>(part, static_cast<__nv_bfloat16*>(dK),
+                                                                                 static_cast<__nv_bfloat16*>(dV), long(n_kv), kv_parts);
+        TA_LAUNCH_CHECK(ctx, "attn_dkv_reduce_kernel");
+    }
     return TA_OK;
 }
 
