@@ -514,15 +514,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) seg_gemm_kernel(const __grid_
                             umma_commit(&empty[stage]);
                             continue;
                         }
+                        // descriptors: built once per k block, advanced by an add per MMA (the start-address field counts
+                        // 16-byte units and cannot carry: shared-memory addresses stay below 256 KB)
+                        const uint64_t bd0 = b_mn ? smem_desc_sw128(sb, 8192, 1024) : smem_desc_sw128(sb, 16, 1024);
+                        const uint64_t ad0 = a_mn ? smem_desc_sw128(sa, 8192, 1024) : smem_desc_sw128(sa, 16, 1024);
+                        const uint64_t b_step = b_mn ? (2048u >> 4) : (32u >> 4), a_step = a_mn ? (2048u >> 4) : (32u >> 4);
                         for (int ki = 0; ki < kinstr; ki++) {
-                            const uint64_t bd = b_mn ? smem_desc_sw128(sb + ki * 2048, 8192, 1024)
-                                                     : smem_desc_sw128(sb + ki * 32, 16, 1024);
 #pragma unroll
-                            for (int hh = 0; hh < MH; hh++) {
-                                const uint64_t ad = a_mn ? smem_desc_sw128(sa + ki * 2048, 8192, 1024)
-                                                         : smem_desc_sw128(sa + hh * 16384 + ki * 32, 16, 1024);
-                                umma_bf16(d_tmem + hh * 256, ad, bd, idesc, acc);
-                            }
+                            for (int hh = 0; hh < MH; hh++)
+                                umma_bf16(d_tmem + hh * 256, ad0 + ki * a_step + (a_mn ? 0u : uint32_t(hh) * (16384u >> 4)), bd0 + ki * b_step, idesc, acc);
                             acc = 1;
                         }
                         umma_commit(&empty[stage]);
