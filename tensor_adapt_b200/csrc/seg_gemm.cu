@@ -750,7 +750,7 @@ done:
 
 // ── CTA-pair kernel, 256 x BN pair tile, double-buffered accumulators ───────
 // The same pairing (cluster of two, tcgen05.mma.cta_group::2 with M = 256, half of every B tile per CTA, no
-// multicast load), but each CTA owns only 128 rows, so one accumulator takes BN <= 256 of its 512 tensor-memory
+// cluster-wide broadcast load), but each CTA owns only 128 rows, so one accumulator takes BN <= 256 of its 512 tensor-memory
 // columns and a second one is free: the epilogue of tile i (TMEM -> registers -> global) overlaps the main loop of
 // tile i+1, which the 256-row single-CTA tiles (all 512 columns in use) cannot do.  Per FLOP a CTA fills the same
 // shared memory as the 256-row kernel and the tensor core reads a third less of it.  One MMA per 16 k (the
