@@ -195,7 +195,9 @@ int ta_swiglu_down_bwd(ta_ctx* ctx, const void* dY, const void* down_w, const vo
  * attention, scale 1/sqrt(head_dim), Q/out [B*T, Hq*hd], K/V [B*T, Hkv*hd]. Instead of the
  * reference's FP32 attn_w[B,Hq,T,T] cache only lse[B,Hq,T] (FP32, natural log) is kept, and the
  * backward also takes the forward output. head_dim 64 or 128. delta_scratch: FP32 [B*Hq*T] or NULL
- * (context scratch). */
+ * (context scratch).  A backward call with fewer than two (128-key tile, KV head, batch) triples per SM shares a
+ * group's query heads out over several CTAs and keeps their FP32 partial dK / dV sums in the context scratch as well
+ * (2 * parts * B*T*Hkv*hd floats, parts <= Hq/Hkv; the scratch grows on first use); results are bit-reproducible. */
 int ta_flash_attn_fwd(ta_ctx* ctx, const void* Q, const void* K, const void* V, void* out, float* lse, int B, int T,
                       int Hq, int Hkv, int head_dim, void* stream);
 int ta_flash_attn_bwd(ta_ctx* ctx, const void* dout, const void* Q, const void* K, const void* V, const void* out,
